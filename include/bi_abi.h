@@ -1,0 +1,127 @@
+/*
+ * C ABI of the B200 batch-invariant kernel library (libbi_b200.so).
+ *
+ * Every entry point is a plain C function over raw device pointers, sizes and
+ * element strides. The library owns no device memory: inputs, outputs and any
+ * scratch ("workspace") are allocated by the caller; the matching
+ * *_workspace_bytes() call says how much scratch an op needs. Launches go to
+ * the caller's stream and never synchronise. The return value is a bi_status;
+ * bi_last_error() gives a thread-local message for the last non-zero status.
+ * Nothing throws or aborts across this boundary.
+ *
+ * The reference project has no C layer: its kernels are Metal source strings
+ * handed to mx.fast.metal_kernel(...) with a grid, a threadgroup size and the
+ * caller-declared output shapes (mlx_batch_invariant/kernels/matmul.py:257-263,
+ * 290-297). Each function below replaces one such kernel call site; the
+ * citation beside it names the reference wrapper whose launch it stands for.
+ */
+#ifndef BI_ABI_H_
+#define BI_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    BI_OK = 0,
+    BI_ERR_UNSUPPORTED = 1, /* shape / dtype / option has no kernel            */
+    BI_ERR_BAD_ARG = 2,     /* null pointer, negative size, inconsistent dims  */
+    BI_ERR_MISALIGNED = 3,  /* pointer or stride not aligned as the op needs   */
+    BI_ERR_WORKSPACE = 4,   /* workspace missing or too small                  */
+    BI_ERR_CUDA = 5,        /* a CUDA runtime / driver call failed             */
+    BI_ERR_DEVICE_WAIT = 6  /* a bounded device-side wait ran out (see bi_read_device_status) */
+} bi_status;
+
+typedef enum { BI_F32 = 0, BI_F16 = 1, BI_BF16 = 2 } bi_dtype;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int bi_version(void);
+
+/* Message for the last non-zero status returned on this thread ("" if none). */
+const char* bi_last_error(void);
+
+/*
+ * Device status word. The tensor-core matmul kernels wait on shared-memory
+ * barriers with an iteration limit; a wait that runs out stores a non-zero
+ * code into *status (an int32 in device memory owned by the caller, zeroed by
+ * the caller) and the kernel returns early instead of hanging. `status` may be
+ * NULL (no reporting). bi_read_device_status copies the word to the host after
+ * synchronising `stream` and returns BI_ERR_DEVICE_WAIT if it is non-zero.
+ */
+int bi_read_device_status(const int32_t* status, int32_t* host_value, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * RMSNorm: out[r, :] = T((x[r, :] * rsqrt(mean(x[r, :]^2) + eps)) * w)       *
+ * replaces batch_invariant_rms_norm / bi_rms_norm                           *
+ * (mlx_batch_invariant/kernels/rmsnorm.py:19-47, 64-79).                    *
+ * x, out: [rows, D] contiguous; w: [D] or NULL (= ones).                    *
+ * ------------------------------------------------------------------------ */
+int bi_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t D, float eps,
+                int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Dense matmul: out[M, N] = a[M, K] @ b[K, N], K folded in 256-wide groups. *
+ * replaces batch_invariant_matmul / launch_tiled / bi_matmul_* /            *
+ * bi_matmul_combine (mlx_batch_invariant/kernels/matmul.py:226-234,         *
+ * 279-340). Strides are in elements. out is [M, N] contiguous.              *
+ * `path` (BI_MATMUL_*) picks the launch shape; AUTO chooses by M. Every     *
+ * path gives the same bits.                                                 *
+ * ------------------------------------------------------------------------ */
+enum { BI_MATMUL_AUTO = 0, BI_MATMUL_SPLIT = 1, BI_MATMUL_FUSED = 2 };
+
+size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+
+int bi_matmul(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes,
+              int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk,
+              int64_t b_sn, int dtype, int path, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Affine quantized matmul: out[M, N] = x[M, K] @ dequant(w)[N, K]^T         *
+ *   dequant(n, k) = T(fma(float(code(n, k)), float(scales[n, k/gs]),        *
+ *                                           float(biases[n, k/gs])))        *
+ * replaces batch_invariant_quantized_matmul / bi_quantized_matmul_*         *
+ * (mlx_batch_invariant/kernels/quantized.py:33-67, 106-125).                *
+ * x: [M, K] row stride x_sm (elements), unit k stride; w: uint32            *
+ * [N, K*bits/32] contiguous, codes packed low to high; scales, biases:      *
+ * [N, K/gs] contiguous in x's dtype; out: [M, N] contiguous, x's dtype.     *
+ * ------------------------------------------------------------------------ */
+size_t bi_qmm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+
+int bi_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
+           void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
+           int group_size, int bits, int dtype, int path, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Decode attention (one query per sequence).                                *
+ * replaces batch_invariant_decode_attention / bi_attn_decode /              *
+ * bi_attn_combine (mlx_batch_invariant/kernels/attention.py:87-171,         *
+ * 326-365). q, out: [B, Hq, 1, D] contiguous. k, v: [B, Hkv, L, D] with     *
+ * element strides (kv_sb, kv_sh, kv_sl) and unit stride along D.            *
+ * kv_lens: optional int32[B] device array of per-sequence key counts        *
+ * (<= L); NULL means every sequence has L keys.                             *
+ * ------------------------------------------------------------------------ */
+size_t bi_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t L, int64_t D, int split_size);
+
+int bi_attn_decode(const void* q, const void* k, const void* v, void* out, const int32_t* kv_lens,
+                   void* workspace, size_t workspace_bytes, int64_t B, int64_t Hq, int64_t Hkv,
+                   int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh, int64_t kv_sl, float scale,
+                   int split_size, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Prefill attention (any number of queries, right-aligned to the cache end  *
+ * when causal). replaces batch_invariant_prefill_attention /                *
+ * bi_attn_prefill (mlx_batch_invariant/kernels/attention.py:173-254,        *
+ * 368-390). q, out: [B, Hq, Tq, D] contiguous; k, v as for decode.          *
+ * ------------------------------------------------------------------------ */
+int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t Hq,
+                    int64_t Hkv, int64_t Tq, int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh,
+                    int64_t kv_sl, float scale, int causal, int split_size, int dtype,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BI_ABI_H_ */

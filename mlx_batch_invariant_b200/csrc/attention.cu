@@ -1,0 +1,497 @@
+// Split-KV attention with a fixed split size, key-by-key online softmax.
+//
+// Canonical order per (batch, head, query) -- the order of the reference's
+// lane-parallel Metal kernels (mlx_batch_invariant/kernels/attention.py:47-85):
+//   * keys run in index order inside fixed splits of `split` keys (256);
+//   * the head dimension is cut into 32 "virtual lanes" of DL = D/32 dims.
+//     Virtual lane v forms part_v = fma chain over its dims of q_hat*k from 0,
+//     q_hat = float(q) * scale. The 32 partials are summed by the xor-butterfly
+//     tree 16, 8, 4, 2, 1:  a_v = part_v + part_{v+16}; b_v = a_v + a_{v+8};
+//     c_v = b_v + b_{v+4}; d_v = c_v + c_{v+2}; s = d_0 + d_1;
+//   * per key: m' = max(m, s); corr = exp(m - m'); p = exp(s - m');
+//     l = fma(l, corr, p); acc_d = fma(acc_d, corr, p * v_d); m = m';
+//     from m = -inf, l = 0, acc = 0 at the start of every split;
+//   * split partials merge left to right: M' = max(M, m); c_old = exp(M - M');
+//     c_new = exp(m - M'); L = fma(L, c_old, l * c_new);
+//     A_d = fma(A_d, c_old, acc_d * c_new); out_d = T(A_d / L).
+//
+// Work layout on the GPU (free to differ, it moves no rounding): eight real
+// lanes -- an "octet" -- carry one key stream. Real lane r owns virtual lanes
+// r, r+8, r+16, r+24, so the first two tree levels are thread-local adds and
+// only levels 4, 2, 1 cross lanes (three shuffles). A warp holds four octets
+// that work on four different units at once.
+//
+// Of the two exponentials of a key step one always has argument exactly 0
+// (m' equals m or s) and exp(0) is exactly 1, so one evaluation of
+// exp(-|s - m|) yields both factors with unchanged bits.
+//
+// decode_kernel and prefill_kernel call the same key_update() and merge
+// functions (merge_coeffs / merge_acc for the split fold), which is why a token's bits do not depend on which of the two
+// produced it.
+#include "bi_common.cuh"
+
+namespace bi {
+namespace {
+
+constexpr int OCT = 8;        // real lanes per key stream
+constexpr int OCT_PER_WARP = 4;
+constexpr int NCHUNK = 4;     // virtual lanes per real lane
+
+template <typename T, int DL> struct alignas(sizeof(T) * DL) Chunk { T v[DL]; };
+
+// Load the 4*DL dims of `row` owned by real lane r, upcast to fp32.
+template <typename T, int DL>
+__device__ __forceinline__ void load_slice(const T* __restrict__ row, int r, float (&dst)[NCHUNK * DL]) {
+    using C = Chunk<T, DL>;
+    const C* p = reinterpret_cast<const C*>(row);
+#pragma unroll
+    for (int j = 0; j < NCHUNK; ++j) {
+        C c = p[r + OCT * j];
+#pragma unroll
+        for (int d = 0; d < DL; ++d) dst[j * DL + d] = Cvt<T>::up(c.v[d]);
+    }
+}
+
+// One key against NQ query rows that share it. `act[iq]` says whether query iq sees the key.
+template <int NQ, int DL>
+__device__ __forceinline__ void key_update(const float (&kf)[NCHUNK * DL], const float (&vf)[NCHUNK * DL],
+                                           const float (&q)[NQ][NCHUNK * DL], float (&m)[NQ], float (&l)[NQ],
+                                           float (&acc)[NQ][NCHUNK * DL], const bool (&act)[NQ]) {
+#pragma unroll
+    for (int iq = 0; iq < NQ; ++iq) {
+        float part[NCHUNK];
+#pragma unroll
+        for (int j = 0; j < NCHUNK; ++j) {
+            float a = 0.0f;
+#pragma unroll
+            for (int d = 0; d < DL; ++d) a = fma_rn(q[iq][j * DL + d], kf[j * DL + d], a);
+            part[j] = a;
+        }
+        // tree level 16 and 8 (thread-local), then 4, 2, 1 across the octet
+        float s = add_rn(add_rn(part[0], part[2]), add_rn(part[1], part[3]));
+        s = add_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
+        s = add_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
+        s = add_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+
+        const float m_old = m[iq];
+        const float m_new = fmaxf(m_old, s);
+        const float e = expf_canon(-fabsf(sub_rn(s, m_old)));
+        const bool rises = s >= m_old;
+        const float corr = rises ? e : 1.0f;
+        const float p = rises ? 1.0f : e;
+        const float l_new = fma_rn(l[iq], corr, p);
+        if (act[iq]) {
+            m[iq] = m_new;
+            l[iq] = l_new;
+#pragma unroll
+            for (int d = 0; d < NCHUNK * DL; ++d) acc[iq][d] = fma_rn(acc[iq][d], corr, mul_rn(p, vf[d]));
+        }
+    }
+}
+
+// Fold one split's (m, l) into the running (M, L) and return the two factors
+// the accumulators are folded with:  A_d = fma(A_d, c_old, acc_d * c_new).
+__device__ __forceinline__ void merge_coeffs(float& M, float& L, float m, float l, float& c_old, float& c_new) {
+    const float M_new = fmaxf(M, m);
+    c_old = expf_canon(sub_rn(M, M_new));
+    c_new = expf_canon(sub_rn(m, M_new));
+    L = fma_rn(L, c_old, mul_rn(l, c_new));
+    M = M_new;
+}
+__device__ __forceinline__ float merge_acc(float A, float c_old, float acc, float c_new) {
+    return fma_rn(A, c_old, mul_rn(acc, c_new));
+}
+
+struct KvLayout {
+    int64_t sb, sh, sl;  // element strides of k and v: batch, kv head, key
+};
+
+// ---- decode: unit = (batch, kv head, chunk of GU query heads, split) ----------
+template <typename T, int DL, int GU>
+__global__ void __launch_bounds__(128) decode_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                     const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
+                                                     float* __restrict__ pm, float* __restrict__ pl,
+                                                     float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
+                                                     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    constexpr int D = 32 * DL;
+    constexpr int NL = NCHUNK * DL;
+    const int lane = threadIdx.x & 31;
+    const int r = lane & (OCT - 1);
+    const long long oct = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * OCT_PER_WARP + (lane >> 3);
+    const long long units = (long long)B * Hkv * nchunk * nsplit;
+    const bool unit_ok = oct < units;
+    long long u = unit_ok ? oct : 0;
+    const int sp = (int)(u % nsplit); u /= nsplit;
+    const int chunk = (int)(u % nchunk); u /= nchunk;
+    const int hk = (int)(u % Hkv); u /= Hkv;
+    const int b = (int)u;
+    const int G = Hq / Hkv;
+    const int h0 = hk * G + chunk * GU;
+    const int gcount = min(GU, G - chunk * GU);
+    const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+    const int j0 = sp * split;
+    const int nk = (unit_ok && j0 < Lb) ? (min(Lb, j0 + split) - j0) : 0;
+
+    const T* kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+    const T* vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+
+    float qf[GU][NL];
+    bool act_head[GU];
+#pragma unroll
+    for (int iq = 0; iq < GU; ++iq) {
+        act_head[iq] = iq < gcount;
+        const T* qr = q + ((int64_t)b * Hq + h0 + min(iq, gcount - 1)) * D;
+        load_slice<T, DL>(qr, r, qf[iq]);
+#pragma unroll
+        for (int d = 0; d < NL; ++d) qf[iq][d] = mul_rn(qf[iq][d], scale);
+    }
+    float m[GU], l[GU], acc[GU][NL];
+#pragma unroll
+    for (int iq = 0; iq < GU; ++iq) {
+        m[iq] = -INFINITY; l[iq] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < NL; ++d) acc[iq][d] = 0.0f;
+    }
+
+    // The trip count is the warp maximum so the shuffles stay converged; an octet
+    // past its own range re-reads its first key and discards the step.
+    int nk_max = nk;
+    nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 8));
+    nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 16));
+    constexpr bool PF = DL < 8;  // keep the next key's rows in registers while this one is processed
+    float kf[NL], vf[NL];
+    if (PF && nk_max > 0) {
+        load_slice<T, DL>(kb, r, kf);
+        load_slice<T, DL>(vb, r, vf);
+    }
+    for (int jj = 0; jj < nk_max; ++jj) {
+        const bool on = jj < nk;
+        bool act[GU];
+#pragma unroll
+        for (int iq = 0; iq < GU; ++iq) act[iq] = on && act_head[iq];
+        if (PF) {
+            float kn[NL], vn[NL];
+            const int jn = (jj + 1 < nk) ? jj + 1 : 0;
+            load_slice<T, DL>(kb + (int64_t)jn * lay.sl, r, kn);
+            load_slice<T, DL>(vb + (int64_t)jn * lay.sl, r, vn);
+            key_update<GU, DL>(kf, vf, qf, m, l, acc, act);
+#pragma unroll
+            for (int d = 0; d < NL; ++d) { kf[d] = kn[d]; vf[d] = vn[d]; }
+        } else {
+            const int jc = on ? jj : 0;
+            load_slice<T, DL>(kb + (int64_t)jc * lay.sl, r, kf);
+            load_slice<T, DL>(vb + (int64_t)jc * lay.sl, r, vf);
+            key_update<GU, DL>(kf, vf, qf, m, l, acc, act);
+        }
+    }
+
+    if (nk > 0) {
+#pragma unroll
+        for (int iq = 0; iq < GU; ++iq) {
+            if (iq < gcount) {
+                const int64_t po = ((int64_t)b * Hq + h0 + iq) * nsplit + sp;
+                if (r == 0) { pm[po] = m[iq]; pl[po] = l[iq]; }
+#pragma unroll
+                for (int j = 0; j < NCHUNK; ++j)
+#pragma unroll
+                    for (int d = 0; d < DL; ++d)
+                        pacc[po * D + (r + OCT * j) * DL + d] = acc[iq][j * DL + d];
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) decode_combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
+                                                             const float* __restrict__ pacc,
+                                                             const int32_t* __restrict__ kv_lens, T* __restrict__ out,
+                                                             int64_t BH, int Hq, int D, int L, int split, int nsplit) {
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= BH * D) return;
+    const int64_t bh = gid / D;
+    const int d = (int)(gid % D);
+    const int b = (int)(bh / Hq);
+    const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+    const int ns = (Lb + split - 1) / split;
+    float M = -INFINITY, Ls = 0.0f, A = 0.0f;
+    for (int i = 0; i < ns; ++i) {
+        const int64_t po = bh * nsplit + i;
+        float c_old, c_new;
+        merge_coeffs(M, Ls, pm[po], pl[po], c_old, c_new);
+        A = merge_acc(A, c_old, pacc[po * D + d], c_new);
+    }
+    out[bh * D + d] = Cvt<T>::down(div_canon(A, Ls));
+}
+
+// ---- prefill: unit = (batch, head, block of QB consecutive queries) -----------
+// QB queries share each K/V row (4, or 2 for the widest heads to stay in registers); which
+// queries are grouped is a launch choice, a query's arithmetic is the same in any group.
+// The running merge state (M, L, A) is touched once per split, so it lives in shared
+// memory, one private slot per thread, and the registers hold the per-key state.
+constexpr int PREFILL_THREADS = 128;
+template <int DL> struct PrefillCfg { static constexpr int QB = DL >= 8 ? 2 : 4; };
+
+template <typename T, int DL>
+__global__ void __launch_bounds__(PREFILL_THREADS) prefill_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                      const T* __restrict__ v, T* __restrict__ out, int B, int Hq,
+                                                      int Hkv, int Tq, int L, KvLayout lay, float scale, int causal,
+                                                      int split) {
+    constexpr int D = 32 * DL;
+    constexpr int NL = NCHUNK * DL;
+    constexpr int QB = PrefillCfg<DL>::QB;
+    extern __shared__ float merge_state[];  // [(QB * (NL + 2))][PREFILL_THREADS]
+    const int lane = threadIdx.x & 31;
+    const int r = lane & (OCT - 1);
+    const int nblk = (Tq + QB - 1) / QB;
+    const long long units = (long long)B * Hq * nblk;
+    const long long oct = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * OCT_PER_WARP + (lane >> 3);
+    const bool unit_ok = oct < units;
+    long long u = unit_ok ? oct : 0;
+    const int blk = (int)(u % nblk); u /= nblk;
+    const int h = (int)(u % Hq); u /= Hq;
+    const int b = (int)u;
+    const int hk = h / (Hq / Hkv);
+    const int q0 = blk * QB;
+
+    const T* kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh;
+    const T* vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh;
+
+    int nkeys[QB];
+    float qf[QB][NL];
+    int nkeys_max = 0;
+#pragma unroll
+    for (int iq = 0; iq < QB; ++iq) {
+        const int qi = min(q0 + iq, Tq - 1);
+        nkeys[iq] = (unit_ok && q0 + iq < Tq) ? (causal ? (L - Tq + qi + 1) : L) : 0;
+        nkeys_max = max(nkeys_max, nkeys[iq]);
+        const T* qr = q + (((int64_t)b * Hq + h) * Tq + qi) * D;
+        load_slice<T, DL>(qr, r, qf[iq]);
+#pragma unroll
+        for (int d = 0; d < NL; ++d) qf[iq][d] = mul_rn(qf[iq][d], scale);
+    }
+    int warp_max = nkeys_max;
+    warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, 8));
+    warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, 16));
+    const int nsplit = (warp_max + split - 1) / split;
+
+    float* const slot = merge_state + threadIdx.x;  // element e of this thread: slot[e * PREFILL_THREADS]
+    constexpr int STRIDE = PREFILL_THREADS;
+    float m[QB], l[QB], acc[QB][NL];
+#pragma unroll
+    for (int iq = 0; iq < QB; ++iq) {
+        slot[(iq * (NL + 2) + 0) * STRIDE] = -INFINITY;
+        slot[(iq * (NL + 2) + 1) * STRIDE] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < NL; ++d) slot[(iq * (NL + 2) + 2 + d) * STRIDE] = 0.0f;
+    }
+
+    for (int sp = 0; sp < nsplit; ++sp) {
+#pragma unroll
+        for (int iq = 0; iq < QB; ++iq) {
+            m[iq] = -INFINITY; l[iq] = 0.0f;
+#pragma unroll
+            for (int d = 0; d < NL; ++d) acc[iq][d] = 0.0f;
+        }
+        const int j0 = sp * split;
+        const int j1 = min(warp_max, j0 + split);
+        constexpr bool PF = DL < 4;  // wider heads have no registers left for a look-ahead row
+        float kf[NL], vf[NL];
+        if (PF) {
+            load_slice<T, DL>(kb + (int64_t)j0 * lay.sl, r, kf);
+            load_slice<T, DL>(vb + (int64_t)j0 * lay.sl, r, vf);
+        }
+        for (int j = j0; j < j1; ++j) {
+            bool act[QB];
+#pragma unroll
+            for (int iq = 0; iq < QB; ++iq) act[iq] = j < nkeys[iq];
+            if (PF) {
+                float kn[NL], vn[NL];
+                const int jn = (j + 1 < j1) ? j + 1 : j0;
+                load_slice<T, DL>(kb + (int64_t)jn * lay.sl, r, kn);
+                load_slice<T, DL>(vb + (int64_t)jn * lay.sl, r, vn);
+                key_update<QB, DL>(kf, vf, qf, m, l, acc, act);
+#pragma unroll
+                for (int d = 0; d < NL; ++d) { kf[d] = kn[d]; vf[d] = vn[d]; }
+            } else {
+                load_slice<T, DL>(kb + (int64_t)j * lay.sl, r, kf);
+                load_slice<T, DL>(vb + (int64_t)j * lay.sl, r, vf);
+                key_update<QB, DL>(kf, vf, qf, m, l, acc, act);
+            }
+        }
+#pragma unroll
+        for (int iq = 0; iq < QB; ++iq) {
+            if (j0 < nkeys[iq]) {
+                float* st = slot + (iq * (NL + 2)) * STRIDE;
+                float Mq = st[0], Lq = st[STRIDE], c_old, c_new;
+                merge_coeffs(Mq, Lq, m[iq], l[iq], c_old, c_new);
+                st[0] = Mq; st[STRIDE] = Lq;
+#pragma unroll
+                for (int d = 0; d < NL; ++d)
+                    st[(2 + d) * STRIDE] = merge_acc(st[(2 + d) * STRIDE], c_old, acc[iq][d], c_new);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int iq = 0; iq < QB; ++iq) {
+        if (unit_ok && q0 + iq < Tq) {
+            T* o = out + (((int64_t)b * Hq + h) * Tq + q0 + iq) * D;
+            using C = Chunk<T, DL>;
+            const float* st = slot + (iq * (NL + 2)) * STRIDE;
+            const float Lq = st[STRIDE];
+#pragma unroll
+            for (int j = 0; j < NCHUNK; ++j) {
+                C c;
+#pragma unroll
+                for (int d = 0; d < DL; ++d) c.v[d] = Cvt<T>::down(div_canon(st[(2 + j * DL + d) * STRIDE], Lq));
+                reinterpret_cast<C*>(o)[r + OCT * j] = c;
+            }
+        }
+    }
+}
+
+int check_common(const char* op, const void* q, const void* k, const void* v, const void* out, int64_t B,
+                 int64_t Hq, int64_t Hkv, int64_t Tq, int64_t L, int64_t D, const KvLayout& lay, int split,
+                 int dtype) {
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "%s: dtype %d", op, dtype);
+    if (B < 0 || Hq <= 0 || Hkv <= 0 || Tq <= 0 || L <= 0 || D <= 0 || split <= 0)
+        return fail(BI_ERR_BAD_ARG, "%s: bad sizes B=%lld Hq=%lld Hkv=%lld Tq=%lld L=%lld D=%lld split=%d", op,
+                    (long long)B, (long long)Hq, (long long)Hkv, (long long)Tq, (long long)L, (long long)D, split);
+    if (Hq % Hkv != 0) return fail(BI_ERR_UNSUPPORTED, "%s: Hq=%lld not a multiple of Hkv=%lld", op, (long long)Hq, (long long)Hkv);
+    if (D != 32 && D != 64 && D != 128 && D != 256)
+        return fail(BI_ERR_UNSUPPORTED, "%s: head_dim %lld (supported: 32, 64, 128, 256)", op, (long long)D);
+    if (B == 0) return BI_OK;
+    if (!q || !k || !v || !out) return fail(BI_ERR_BAD_ARG, "%s: null pointer", op);
+    const size_t cb = (size_t)(D / 32) * dtype_size(dtype);  // bytes of one chunk load
+    const size_t al = cb > 16 ? 16 : cb;
+    if (!aligned(q, al) || !aligned(k, al) || !aligned(v, al) || !aligned(out, al))
+        return fail(BI_ERR_MISALIGNED, "%s: pointers must be %zu-byte aligned", op, al);
+    const int64_t se = (int64_t)(al / dtype_size(dtype));
+    if (se > 1 && (lay.sb % se || lay.sh % se || lay.sl % se))
+        return fail(BI_ERR_MISALIGNED, "%s: k/v strides must be multiples of %lld elements", op, (long long)se);
+    if (lay.sl < D) return fail(BI_ERR_BAD_ARG, "%s: key stride %lld < head_dim", op, (long long)lay.sl);
+    if (L > (1 << 30) || B * Hq * Tq > (1LL << 40))
+        return fail(BI_ERR_UNSUPPORTED, "%s: problem too large", op);
+    return BI_OK;
+}
+
+template <typename T, int DL>
+int launch_decode(const void* q, const void* k, const void* v, void* out, const int32_t* kv_lens, float* ws,
+                  int64_t B, int64_t Hq, int64_t Hkv, int64_t L, const KvLayout& lay, float scale, int split,
+                  cudaStream_t st) {
+    constexpr int D = 32 * DL;
+    const int G = (int)(Hq / Hkv);
+    const int nsplit = (int)((L + split - 1) / split);
+    const int64_t BH = B * Hq;
+    float* pm = ws;
+    float* pl = pm + BH * nsplit;
+    float* pacc = pl + BH * nsplit;
+    // Query heads of a kv head share each K/V row load, up to four per unit.
+    // How they are grouped is a launch choice; a head's arithmetic is the same alone or grouped.
+    const int GU = (G >= 4 && DL < 8) ? 4 : (G >= 2 ? 2 : 1);
+    const int nchunk = (G + GU - 1) / GU;
+    const int64_t units = B * Hkv * nchunk * nsplit;
+    const int warps = 4;
+    const int64_t blocks = (units + warps * OCT_PER_WARP - 1) / (warps * OCT_PER_WARP);
+    if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode: grid too large");
+    const T* qp = static_cast<const T*>(q);
+    const T* kp = static_cast<const T*>(k);
+    const T* vp = static_cast<const T*>(v);
+    dim3 grid((unsigned)blocks), block(32 * warps);
+#define BI_DECODE_LAUNCH(GUV)                                                                              \
+    decode_kernel<T, DL, GUV><<<grid, block, 0, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
+                                                      (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk)
+    if (GU == 4) {
+        if constexpr (DL < 8) BI_DECODE_LAUNCH(4);
+    } else if (GU == 2) {
+        BI_DECODE_LAUNCH(2);
+    } else {
+        BI_DECODE_LAUNCH(1);
+    }
+#undef BI_DECODE_LAUNCH
+    int rc = check_launch("bi_attn_decode");
+    if (rc) return rc;
+    const int64_t n2 = BH * D;
+    decode_combine_kernel<T><<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
+    return check_launch("bi_attn_decode combine");
+}
+
+template <typename T, int DL>
+int launch_prefill(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t Hq, int64_t Hkv,
+                   int64_t Tq, int64_t L, const KvLayout& lay, float scale, int causal, int split, cudaStream_t st) {
+    constexpr int QB = PrefillCfg<DL>::QB;
+    const int64_t nblk = (Tq + QB - 1) / QB;
+    const int64_t units = B * Hq * nblk;
+    constexpr int warps = PREFILL_THREADS / 32;
+    const int64_t blocks = (units + warps * OCT_PER_WARP - 1) / (warps * OCT_PER_WARP);
+    if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_attn_prefill: grid too large");
+    const size_t smem = (size_t)QB * (NCHUNK * DL + 2) * PREFILL_THREADS * sizeof(float);
+    auto kern = prefill_kernel<T, DL>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_prefill smem attr: %s", cudaGetErrorString(e));
+    }
+    kern<<<(unsigned)blocks, PREFILL_THREADS, smem, st>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(out), (int)B,
+        (int)Hq, (int)Hkv, (int)Tq, (int)L, lay, scale, causal, split);
+    return check_launch("bi_attn_prefill");
+}
+
+}  // namespace
+}  // namespace bi
+
+#define BI_DISPATCH_T_DL(FN, ...)                                                        \
+    do {                                                                                 \
+        const int dl_ = (int)(D / 32);                                                   \
+        if (dtype == BI_F32) {                                                           \
+            if (dl_ == 1) return FN<float, 1>(__VA_ARGS__);                              \
+            if (dl_ == 2) return FN<float, 2>(__VA_ARGS__);                              \
+            if (dl_ == 4) return FN<float, 4>(__VA_ARGS__);                              \
+            return FN<float, 8>(__VA_ARGS__);                                            \
+        } else if (dtype == BI_F16) {                                                    \
+            if (dl_ == 1) return FN<__half, 1>(__VA_ARGS__);                             \
+            if (dl_ == 2) return FN<__half, 2>(__VA_ARGS__);                             \
+            if (dl_ == 4) return FN<__half, 4>(__VA_ARGS__);                             \
+            return FN<__half, 8>(__VA_ARGS__);                                           \
+        } else {                                                                         \
+            if (dl_ == 1) return FN<__nv_bfloat16, 1>(__VA_ARGS__);                      \
+            if (dl_ == 2) return FN<__nv_bfloat16, 2>(__VA_ARGS__);                      \
+            if (dl_ == 4) return FN<__nv_bfloat16, 4>(__VA_ARGS__);                      \
+            return FN<__nv_bfloat16, 8>(__VA_ARGS__);                                    \
+        }                                                                                \
+    } while (0)
+
+extern "C" size_t bi_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t L, int64_t D, int split_size) {
+    if (B <= 0 || Hq <= 0 || L <= 0 || D <= 0 || split_size <= 0) return 0;
+    const int64_t nsplit = (L + split_size - 1) / split_size;
+    return (size_t)(B * Hq * nsplit * (D + 2)) * sizeof(float);
+}
+
+extern "C" int bi_attn_decode(const void* q, const void* k, const void* v, void* out, const int32_t* kv_lens,
+                              void* workspace, size_t workspace_bytes, int64_t B, int64_t Hq, int64_t Hkv, int64_t L,
+                              int64_t D, int64_t kv_sb, int64_t kv_sh, int64_t kv_sl, float scale, int split_size,
+                              int dtype, void* stream) {
+    using namespace bi;
+    KvLayout lay{kv_sb, kv_sh, kv_sl};
+    int rc = check_common("bi_attn_decode", q, k, v, out, B, Hq, Hkv, 1, L, D, lay, split_size, dtype);
+    if (rc || B == 0) return rc;
+    const size_t need = bi_attn_decode_workspace_bytes(B, Hq, L, D, split_size);
+    if (!workspace || workspace_bytes < need)
+        return fail(BI_ERR_WORKSPACE, "bi_attn_decode: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if (!aligned(workspace, 16)) return fail(BI_ERR_MISALIGNED, "bi_attn_decode: workspace must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* ws = static_cast<float*>(workspace);
+    BI_DISPATCH_T_DL(launch_decode, q, k, v, out, kv_lens, ws, B, Hq, Hkv, L, lay, scale, split_size, st);
+}
+
+extern "C" int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t Hq,
+                               int64_t Hkv, int64_t Tq, int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh,
+                               int64_t kv_sl, float scale, int causal, int split_size, int dtype, void* stream) {
+    using namespace bi;
+    KvLayout lay{kv_sb, kv_sh, kv_sl};
+    int rc = check_common("bi_attn_prefill", q, k, v, out, B, Hq, Hkv, Tq, L, D, lay, split_size, dtype);
+    if (rc || B == 0) return rc;
+    if (causal && Tq > L) return fail(BI_ERR_BAD_ARG, "bi_attn_prefill: causal needs Tq <= L (Tq=%lld L=%lld)", (long long)Tq, (long long)L);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    BI_DISPATCH_T_DL(launch_prefill, q, k, v, out, B, Hq, Hkv, Tq, L, lay, scale, causal, split_size, st);
+}

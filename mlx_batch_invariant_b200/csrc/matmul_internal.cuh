@@ -1,0 +1,34 @@
+// Launchers shared between the matmul translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bi {
+
+// Split-path fold: out[i] = T(((0 + part[0][i]) + part[1][i]) + ...), part is [G][MN] fp32.
+int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st);
+
+// CUDA-core path (fp32 inputs, or weights TMA cannot address).
+int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,
+                       int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, bool split,
+                       cudaStream_t st);
+int launch_simt_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out, float* part,
+                    int64_t M, int64_t N, int64_t K, int64_t x_sm, int gs, int bits, int dtype, bool split,
+                    cudaStream_t st);
+
+// Tensor-core path (tcgen05 / TMEM / TMA), 16-bit inputs. `w_kn` describes the weight:
+// dense -> pointer to W[N, K] rows with row stride w_ld elements; quantized -> packed codes.
+struct TcQuant {
+    const uint32_t* codes;  // nullptr for the dense kernel
+    const void* scales;
+    const void* biases;
+    int bits, gs;
+};
+// Returns true when the tensor-core path can take this weight / activation layout.
+bool tc_matmul_supported(const void* x, int64_t x_ld, const void* w, int64_t w_ld, int64_t N, int64_t K, int dtype,
+                         const TcQuant* q);
+int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, const TcQuant* q, void* out,
+                     float* part, int64_t M, int64_t N, int64_t K, int dtype, bool split, int32_t* status,
+                     cudaStream_t st);
+
+}  // namespace bi

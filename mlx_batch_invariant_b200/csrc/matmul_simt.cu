@@ -1,0 +1,220 @@
+// CUDA-core matmul with the K-group contract, and the split-path combine kernel.
+//
+// Canonical order per output element on this path:
+//   for each K group g (256 wide, ascending):  acc = 0;
+//       for k ascending inside the group:      acc = fma(a[m,k], b[k,n], acc)
+//   total = 0;  total = total + acc_g          (plain fp32 adds, g ascending)
+//   out = T(total)                             (one rounding)
+// Operands are upcast to fp32 exactly; every product/sum is a single fp32 fma.
+// It serves fp32 inputs (Blackwell tensor cores have no full-precision fp32
+// mode) and 16-bit weights whose rows cannot be described to TMA. Which path a
+// weight takes depends on the weight alone, never on the batch.
+//
+// Two launch shapes, as in the reference (mlx_batch_invariant/kernels/matmul.py:279-314):
+// fused (one CTA walks all groups and folds) and split (grid.z = group, raw fp32
+// partials, then combine_kernel folds them). Both perform the same sequence of
+// operations on every element.
+#include "bi_common.cuh"
+#include "matmul_internal.cuh"
+
+namespace bi {
+namespace {
+
+constexpr int BN = 64;
+constexpr int BK = 16;
+constexpr int THREADS = 256;
+
+// Affine dequantization of one code: fma in fp32, then one rounding to the staged type T.
+template <typename T>
+__device__ __forceinline__ float dequant_code(uint32_t code, float s, float b) {
+    return Cvt<T>::up(Cvt<T>::down(fma_rn((float)code, s, b)));
+}
+
+struct QuantArgs {
+    const uint32_t* w;   // [N, K*bits/32]
+    const void* scales;  // [N, K/gs]
+    const void* biases;
+    int bits, gs;
+};
+
+// TM rows x 4 columns per thread; tile = (16*TM) x 64.
+template <typename T, int TM, bool SPLIT, bool QUANT>
+__global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                              QuantArgs qa, void* __restrict__ outp, int M, int N,
+                                                              int K, int64_t a_sm, int64_t a_sk, int64_t b_sk,
+                                                              int64_t b_sn) {
+    constexpr int BM = 16 * TM;
+    __shared__ float As[BK][BM];
+    __shared__ float Bs[BK][BN];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int ngroups = (K + GROUP_K - 1) / GROUP_K;
+    const int g0 = SPLIT ? (int)blockIdx.z : 0;
+    const int g1 = SPLIT ? g0 + 1 : ngroups;
+
+    float total[TM][4];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
+
+    for (int g = g0; g < g1; ++g) {
+        float acc[TM][4];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        const int kg0 = g * GROUP_K;
+        const int kg1 = min(K, kg0 + GROUP_K);
+        for (int k0 = kg0; k0 < kg1; k0 += BK) {
+            const int kc = min(BK, kg1 - k0);
+            // stage A: k fastest when a is k-contiguous, else m fastest
+            for (int e = tid; e < BM * BK; e += THREADS) {
+                int kk, i;
+                if (a_sk == 1) { kk = e % BK; i = e / BK; } else { i = e % BM; kk = e / BM; }
+                const int m = m0 + i, k = k0 + kk;
+                As[kk][i] = (m < M && kk < kc) ? Cvt<T>::up(a[(int64_t)m * a_sm + (int64_t)k * a_sk]) : 0.0f;
+            }
+            for (int e = tid; e < BN * BK; e += THREADS) {
+                int kk, j;
+                if (QUANT || b_sk == 1) { kk = e % BK; j = e / BK; } else { j = e % BN; kk = e / BN; }
+                const int n = n0 + j, k = k0 + kk;
+                float v = 0.0f;
+                if (n < N && kk < kc) {
+                    if (QUANT) {
+                        const int per_word = 32 / qa.bits;
+                        const uint32_t word = qa.w[(int64_t)n * (K / per_word) + k / per_word];
+                        const uint32_t code = (word >> ((k % per_word) * qa.bits)) & ((1u << qa.bits) - 1u);
+                        const int64_t gi = (int64_t)n * (K / qa.gs) + k / qa.gs;
+                        const float s = Cvt<T>::up(static_cast<const T*>(qa.scales)[gi]);
+                        const float bb = Cvt<T>::up(static_cast<const T*>(qa.biases)[gi]);
+                        v = dequant_code<T>(code, s, bb);
+                    } else {
+                        v = Cvt<T>::up(b[(int64_t)k * b_sk + (int64_t)n * b_sn]);
+                    }
+                }
+                Bs[kk][j] = v;
+            }
+            __syncthreads();
+            for (int kk = 0; kk < kc; ++kk) {
+                float av[TM], bv[4];
+#pragma unroll
+                for (int i = 0; i < TM; ++i) av[i] = As[kk][ty * TM + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < TM; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = fma_rn(av[i], bv[j], acc[i][j]);
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) total[i][j] = SPLIT ? acc[i][j] : add_rn(total[i][j], acc[i][j]);
+    }
+
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (SPLIT) static_cast<float*>(outp)[((int64_t)g0 * M + m) * N + n] = total[i][j];
+            else static_cast<T*>(outp)[(int64_t)m * N + n] = Cvt<T>::down(total[i][j]);
+        }
+    }
+}
+
+// out[idx] = T(((0 + p_0[idx]) + p_1[idx]) + ...): the fold of the split path
+// (reference: bi_matmul_combine, mlx_batch_invariant/kernels/matmul.py:226-234).
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ part, T* __restrict__ out, int G,
+                                                      int64_t MN) {
+    const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (i0 >= MN) return;
+    float total[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) total[v] = 0.0f;
+    for (int g = 0; g < G; ++g) {
+        const float* p = part + (int64_t)g * MN + i0;
+        if (VEC == 4) {
+            const float4 x = *reinterpret_cast<const float4*>(p);
+            total[0] = add_rn(total[0], x.x); total[1 % VEC] = add_rn(total[1 % VEC], x.y);
+            total[2 % VEC] = add_rn(total[2 % VEC], x.z); total[3 % VEC] = add_rn(total[3 % VEC], x.w);
+        } else {
+            total[0] = add_rn(total[0], p[0]);
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) out[i0 + v] = Cvt<T>::down(total[v]);
+}
+
+template <typename T>
+int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st) {
+    if (MN % 4 == 0 && aligned(part, 16)) {
+        const int64_t threads = MN / 4;
+        combine_kernel<T, 4><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN);
+    } else {
+        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN);
+    }
+    return check_launch("matmul combine");
+}
+
+template <typename T, bool QUANT>
+int simt_t(const void* a, const void* b, const QuantArgs& qa, void* out, float* part, int64_t M, int64_t N,
+           int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, bool split, cudaStream_t st) {
+    const int G = (int)((K + GROUP_K - 1) / GROUP_K);
+    const bool skinny = M <= 16;
+    const int BM = skinny ? 16 : 64;
+    dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), split ? G : 1);
+    if (grid.y > 65535) return fail(BI_ERR_UNSUPPORTED, "matmul (cuda-core path): M=%lld too large", (long long)M);
+    const T* ap = static_cast<const T*>(a);
+    const T* bp = static_cast<const T*>(b);
+    void* dst = split ? static_cast<void*>(part) : out;
+#define BI_SIMT(TMV, SP) simt_matmul_kernel<T, TMV, SP, QUANT><<<grid, THREADS, 0, st>>>(ap, bp, qa, dst, (int)M, (int)N, (int)K, a_sm, a_sk, b_sk, b_sn)
+    if (skinny) { if (split) BI_SIMT(1, true); else BI_SIMT(1, false); }
+    else        { if (split) BI_SIMT(4, true); else BI_SIMT(4, false); }
+#undef BI_SIMT
+    int rc = check_launch("matmul (cuda-core path)");
+    if (rc || !split) return rc;
+    return combine_t<T>(part, out, G, M * N, st);
+}
+
+}  // namespace
+
+int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st) {
+    switch (dtype) {
+        case BI_F32: return combine_t<float>(part, out, G, MN, st);
+        case BI_F16: return combine_t<__half>(part, out, G, MN, st);
+        default:     return combine_t<__nv_bfloat16>(part, out, G, MN, st);
+    }
+}
+
+int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,
+                       int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, bool split,
+                       cudaStream_t st) {
+    QuantArgs qa{nullptr, nullptr, nullptr, 0, 0};
+    switch (dtype) {
+        case BI_F32: return simt_t<float, false>(a, b, qa, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, split, st);
+        case BI_F16: return simt_t<__half, false>(a, b, qa, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, split, st);
+        default:     return simt_t<__nv_bfloat16, false>(a, b, qa, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, split, st);
+    }
+}
+
+int launch_simt_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out, float* part,
+                    int64_t M, int64_t N, int64_t K, int64_t x_sm, int gs, int bits, int dtype, bool split,
+                    cudaStream_t st) {
+    QuantArgs qa{w, scales, biases, bits, gs};
+    switch (dtype) {
+        case BI_F32: return simt_t<float, true>(x, nullptr, qa, out, part, M, N, K, x_sm, 1, 1, K, split, st);
+        case BI_F16: return simt_t<__half, true>(x, nullptr, qa, out, part, M, N, K, x_sm, 1, 1, K, split, st);
+        default:     return simt_t<__nv_bfloat16, true>(x, nullptr, qa, out, part, M, N, K, x_sm, 1, 1, K, split, st);
+    }
+}
+
+}  // namespace bi

@@ -1,0 +1,127 @@
+// RMSNorm, one CTA of 256 threads per row.
+//
+// Canonical order per row (identical to the Metal kernel of the reference,
+// mlx_batch_invariant/kernels/rmsnorm.py:19-47):
+//   thread t:  ss_t = 0; for i = t, t+256, ...: ss_t = fma(x_i, x_i, ss_t)
+//   tree:      for s = 128, 64, ..., 1: red[t] = red[t] + red[t+s]  (t < s)
+//   inv  = 1 / sqrt(red[0] / float(D) + eps)
+//   out_i = T((x_i * inv) * w_i)          two fp32 multiplies, one rounding
+// How many rows share the launch never enters: a row sees only its own CTA.
+//
+// Data movement is free to differ from the reference: the row is staged in
+// shared memory with 16-byte loads, each thread then walks its stride-256
+// elements there, results are written back in place and leave with 16-byte
+// stores. Rows too long for shared memory, or not 16-byte aligned, take the
+// same arithmetic straight from global memory.
+#include "bi_common.cuh"
+
+namespace bi {
+namespace {
+
+constexpr int TG = 256;
+
+__device__ __forceinline__ float block_tree_sum(float ss, float* red, int t) {
+    red[t] = ss;
+    __syncthreads();
+    if (t < 128) red[t] = add_rn(red[t], red[t + 128]);
+    __syncthreads();
+    if (t < 64) red[t] = add_rn(red[t], red[t + 64]);
+    __syncthreads();
+    if (t < 32) {
+        float v = add_rn(red[t], red[t + 32]);
+        v = add_rn(v, __shfl_down_sync(0xffffffffu, v, 16));
+        v = add_rn(v, __shfl_down_sync(0xffffffffu, v, 8));
+        v = add_rn(v, __shfl_down_sync(0xffffffffu, v, 4));
+        v = add_rn(v, __shfl_down_sync(0xffffffffu, v, 2));
+        v = add_rn(v, __shfl_down_sync(0xffffffffu, v, 1));
+        if (t == 0) red[0] = v;
+    }
+    __syncthreads();
+    return red[0];
+}
+
+template <typename T, bool STAGED, bool HAS_W>
+__global__ void __launch_bounds__(TG) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                      T* __restrict__ out, int D, float eps) {
+    extern __shared__ uint4 stage_raw[];
+    __shared__ float red[TG];
+    const int t = threadIdx.x;
+    const size_t row = blockIdx.x;
+    const T* xr = x + row * (size_t)D;
+    T* orow = out + row * (size_t)D;
+    T* xs = reinterpret_cast<T*>(stage_raw);
+
+    if (STAGED) {
+        constexpr int VEC = 16 / sizeof(T);
+        const uint4* src = reinterpret_cast<const uint4*>(xr);
+        for (int i = t; i < D / VEC; i += TG) stage_raw[i] = __ldg(src + i);
+        __syncthreads();
+    }
+    const T* xin = STAGED ? xs : xr;
+
+    float ss = 0.0f;
+    for (int i = t; i < D; i += TG) {
+        float v = Cvt<T>::up(xin[i]);
+        ss = fma_rn(v, v, ss);
+    }
+    const float total = block_tree_sum(ss, red, t);
+    const float inv = rsqrt_canon(add_rn(div_canon(total, (float)D), eps));
+
+    for (int i = t; i < D; i += TG) {
+        float v = mul_rn(Cvt<T>::up(xin[i]), inv);
+        float wi = HAS_W ? Cvt<T>::up(w[i]) : 1.0f;
+        T o = Cvt<T>::down(mul_rn(v, wi));
+        if (STAGED) xs[i] = o; else orow[i] = o;
+    }
+    if (STAGED) {
+        constexpr int VEC = 16 / sizeof(T);
+        __syncthreads();
+        uint4* dst = reinterpret_cast<uint4*>(orow);
+        for (int i = t; i < D / VEC; i += TG) dst[i] = stage_raw[i];
+    }
+}
+
+template <typename T>
+int launch(const void* x, const void* w, void* out, int64_t rows, int64_t D, float eps, cudaStream_t st) {
+    const size_t row_bytes = (size_t)D * sizeof(T);
+    const bool staged = row_bytes % 16 == 0 && row_bytes <= 160 * 1024 && aligned(x, 16) && aligned(out, 16);
+    const T* xp = static_cast<const T*>(x);
+    const T* wp = static_cast<const T*>(w);
+    T* op = static_cast<T*>(out);
+    dim3 grid((unsigned)rows), block(TG);
+#define BI_RMS_LAUNCH(ST, HW)                                                                       \
+    do {                                                                                            \
+        auto kern = rms_norm_kernel<T, ST, HW>;                                                     \
+        size_t smem = ST ? row_bytes : 0;                                                           \
+        if (smem > 48 * 1024) {                                                                     \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)smem);                                        \
+            if (e != cudaSuccess) return fail(BI_ERR_CUDA, "rms_norm smem attr: %s",               \
+                                              cudaGetErrorString(e));                               \
+        }                                                                                           \
+        kern<<<grid, block, smem, st>>>(xp, wp, op, (int)D, eps);                                   \
+    } while (0)
+    if (staged) { if (w) BI_RMS_LAUNCH(true, true); else BI_RMS_LAUNCH(true, false); }
+    else        { if (w) BI_RMS_LAUNCH(false, true); else BI_RMS_LAUNCH(false, false); }
+#undef BI_RMS_LAUNCH
+    return check_launch("bi_rms_norm");
+}
+
+}  // namespace
+}  // namespace bi
+
+extern "C" int bi_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t D, float eps,
+                           int dtype, void* stream) {
+    using namespace bi;
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_rms_norm: dtype %d", dtype);
+    if (rows < 0 || D <= 0 || D > INT32_MAX) return fail(BI_ERR_BAD_ARG, "bi_rms_norm: rows=%lld D=%lld", (long long)rows, (long long)D);
+    if (rows == 0) return BI_OK;
+    if (!x || !out) return fail(BI_ERR_BAD_ARG, "bi_rms_norm: null pointer");
+    if (rows > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_rms_norm: rows=%lld exceeds the grid limit", (long long)rows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case BI_F32: return launch<float>(x, w, out, rows, D, eps, st);
+        case BI_F16: return launch<__half>(x, w, out, rows, D, eps, st);
+        default:     return launch<__nv_bfloat16>(x, w, out, rows, D, eps, st);
+    }
+}

@@ -1,0 +1,24 @@
+"""Batch-invariant kernels for B200 (host wrappers over the C ABI).
+
+One rule, as in the reference (mlx_batch_invariant/kernels/__init__.py:3-10): the
+floating-point reduction order of an output element never depends on how many
+other rows or sequences share the launch.
+"""
+
+from .matmul import batch_invariant_matmul
+from .rmsnorm import batch_invariant_rms_norm
+from .quantized import batch_invariant_quantized_matmul
+from .attention import (
+    batch_invariant_attention,
+    batch_invariant_decode_attention,
+    batch_invariant_prefill_attention,
+)
+
+__all__ = [
+    "batch_invariant_matmul",
+    "batch_invariant_rms_norm",
+    "batch_invariant_quantized_matmul",
+    "batch_invariant_decode_attention",
+    "batch_invariant_prefill_attention",
+    "batch_invariant_attention",
+]

@@ -1,0 +1,76 @@
+"""Batch-invariant dense matmul ``a @ b`` for 2-D ``b`` (host wrapper).
+
+Mirrors batch_invariant_matmul / launch_tiled of the reference
+(mlx_batch_invariant/kernels/matmul.py:279-340): K is cut into fixed groups of
+GROUP_K = 256, each group partial starts from zero, the fp32 partials are folded
+left to right, and the launch shape (split: one CTA per K group plus a combine
+kernel; fused: one CTA folds all groups) depends on M while the arithmetic does not.
+``b`` is read through its strides, so the ``W.T`` view nn.Linear passes is consumed
+in place.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._util import adopt, dtype_code, give_back, require_cuda, rows_16b
+
+GROUP_K = 256
+
+_PATHS = {"auto": _lib.PATH_AUTO, "split": _lib.PATH_SPLIT, "fused": _lib.PATH_FUSED}
+
+
+def _workspace(nbytes: int, dev: torch.device) -> torch.Tensor | None:
+    return torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+
+
+def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
+    """The predicate bi_matmul applies to the weight (16-bit, rows of K contiguous elements
+    that TMA can address). Used only to decide whether the activation needs an aligned copy."""
+    es = b.element_size()
+    return (b.dtype != torch.float32 and b.stride(0) == 1 and K % 8 == 0 and b.data_ptr() % 16 == 0
+            and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
+
+
+def batch_invariant_matmul(a, b, *, path: str = "auto"):
+    """``a @ b`` with a batch-invariant reduction order.
+
+    ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
+    view is fine). fp32 accumulation; the output dtype is the promoted input dtype.
+    ``path`` ("auto", "split", "fused") forces a launch shape; all give the same bits.
+    """
+    at, foreign = adopt(a)
+    bt, _ = adopt(b)
+    if bt.ndim != 2:
+        raise ValueError("batch_invariant_matmul: b must be 2-D")
+    if at.ndim < 1:
+        raise ValueError("batch_invariant_matmul: a must have at least one dim")
+    lead = at.shape[:-1]
+    K = at.shape[-1]
+    if K != bt.shape[0]:
+        raise ValueError(f"shape mismatch {tuple(at.shape)} @ {tuple(bt.shape)}")
+    dev = require_cuda(at, bt)
+    N = bt.shape[1]
+    out_dtype = torch.result_type(at, bt)
+    code = dtype_code(out_dtype)
+    a2 = at.reshape(-1, K)
+    if a2.dtype != out_dtype:
+        a2 = a2.to(out_dtype)
+    if bt.dtype != out_dtype:
+        bt = bt.to(out_dtype)
+    M = a2.shape[0]
+    if K == 0:
+        return give_back(torch.zeros((*lead, N), dtype=out_dtype, device=dev), a, foreign)
+    if M > 0 and _weight_is_tensor_core(bt, K):
+        a2 = rows_16b(a2)
+    out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    lib = _lib.load()
+    G = (K + GROUP_K - 1) // GROUP_K
+    nbytes = G * M * N * 4 if path == "split" else lib.bi_matmul_workspace_bytes(M, N, K, code)
+    ws = _workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.bi_matmul(a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
+                                 a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code,
+                                 _PATHS[path], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+    return give_back(out.reshape(*lead, N), a, foreign)

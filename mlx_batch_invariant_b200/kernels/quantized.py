@@ -1,0 +1,70 @@
+"""Batch-invariant affine quantized matmul ``y[M, N] = x[M, K] @ W[N, K].T`` (host wrapper).
+
+``W`` is the packed affine format of the reference (mlx_batch_invariant/kernels/quantized.py:3-7):
+``bits``-wide unsigned codes packed low to high in uint32 words, one scale and bias
+per ``group_size`` consecutive codes of a row::
+
+    w[n, k] = code(n, k) * scales[n, k // group_size] + biases[n, k // group_size]
+
+The kernel dequantizes while it stages the weight tile (fp32 fma, one rounding to the
+input dtype) and then runs the dense kernel's MMA sequence and fold.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ._util import adopt, dtype_code, give_back, require_cuda, rows_16b
+from .matmul import GROUP_K, _PATHS, _workspace
+
+SUPPORTED_BITS = (4, 8)
+SUPPORTED_GROUPS = (32, 64, 128)
+
+
+def supports(x, w, scales, biases, transpose, group_size, bits, mode) -> bool:
+    """Same predicate as the reference (mlx_batch_invariant/kernels/quantized.py:91-103)."""
+    return (
+        mode == "affine"
+        and bool(transpose)
+        and biases is not None
+        and bits in SUPPORTED_BITS
+        and group_size in SUPPORTED_GROUPS
+        and isinstance(x, torch.Tensor) and x.is_floating_point() and x.dtype in _lib.DTYPE_CODE
+        and isinstance(w, torch.Tensor) and w.dtype in (torch.uint32, torch.int32) and w.ndim == 2
+        and scales.ndim == 2 and biases.ndim == 2
+        and x.shape[-1] % group_size == 0
+        and w.shape[1] * (32 // bits) == x.shape[-1]
+    )
+
+
+def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, bits: int, path: str = "auto"):
+    xt, foreign = adopt(x)
+    wt, st, bt = adopt(w)[0], adopt(scales)[0], adopt(biases)[0]
+    dev = require_cuda(xt, wt, st, bt)
+    if bits not in SUPPORTED_BITS or group_size not in SUPPORTED_GROUPS:
+        raise ValueError(f"unsupported quantization: bits={bits}, group_size={group_size}")
+    lead = xt.shape[:-1]
+    K = xt.shape[-1]
+    N = wt.shape[0]
+    if wt.ndim != 2 or wt.shape[1] * (32 // bits) != K:
+        raise ValueError(f"packed weight shape {tuple(wt.shape)} does not match K={K} at {bits} bits")
+    if K % group_size or st.shape != (N, K // group_size) or bt.shape != st.shape:
+        raise ValueError(f"scales/biases shape {tuple(st.shape)} does not match (N={N}, K/group_size={K // group_size})")
+    dt = xt.dtype
+    code = dtype_code(dt)
+    x2 = rows_16b(xt.reshape(-1, K))
+    M = x2.shape[0]
+    st = st.to(dt).contiguous()
+    bt = bt.to(dt).contiguous()
+    wt = wt.contiguous()
+    out = torch.empty((M, N), dtype=dt, device=dev)
+    lib = _lib.load()
+    G = (K + GROUP_K - 1) // GROUP_K
+    nbytes = G * M * N * 4 if path == "split" else lib.bi_qmm_workspace_bytes(M, N, K, code)
+    ws = _workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.bi_qmm(x2.data_ptr(), wt.data_ptr(), st.data_ptr(), bt.data_ptr(), out.data_ptr(),
+                              _lib.ptr(ws), nbytes, M, N, K, x2.stride(0) if M > 1 else K, group_size, bits, code,
+                              _PATHS[path], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+    return give_back(out.reshape(*lead, N), x, foreign)

@@ -1,0 +1,175 @@
+"""Dense and quantized matmul on the GPU, through the C ABI.
+
+The CUDA-core path (fp32, or weights TMA cannot address) is bit-exact against the CPU oracle.
+The tensor-core path cannot be reproduced on a CPU (the MMA's internal order is the hardware's):
+it is held to the float64 semantics by tolerance and to itself bit for bit -- split == fused,
+every batch size, every row position of the 128-row tile, quantized == dense on the
+oracle-dequantized weight."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference as R
+from tests.golden import make_golden
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def xw(M, N, K, dt, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(M, K, generator=g).to(dt), (torch.randn(N, K, generator=g) / K ** 0.5).to(dt)
+
+
+# ---- CUDA-core path -----------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 256), (3, 33, 600), (17, 70, 257), (40, 130, 1000), (5, 8, 16)])
+@pytest.mark.parametrize("path", ["auto", "split", "fused"])
+def test_fp32_bit_exact_vs_oracle(bi, M, N, K, path):
+    x, w = xw(M, N, K, torch.float32, M + N + K)
+    got = bi.batch_invariant_matmul(x.cuda(), w.cuda().T, path=path)
+    assert R.bits_of(got) == R.bits_of(R.matmul_f32order(x, w.T.contiguous()))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_16bit_weight_tma_cannot_address_takes_cuda_core_order(bi, dt):
+    x, w = xw(6, 40, 300 + 3, dt, 9)         # K % 8 != 0
+    got = bi.batch_invariant_matmul(x.cuda(), w.cuda().T)
+    assert R.bits_of(got) == R.bits_of(R.matmul_f32order(x, w.T.contiguous()))
+    xb, wb = xw(4, 24, 64, dt, 10)           # row-major [K, N] operand (not a W.T view)
+    got = bi.batch_invariant_matmul(xb.cuda(), wb.T.contiguous().cuda())
+    assert R.bits_of(got) == R.bits_of(R.matmul_f32order(xb, wb.T.contiguous()))
+
+
+@pytest.mark.parametrize("name", ["f32"])
+def test_golden_fixture_fp32(bi, name):
+    gold = np.load(make_golden.OUT)
+    i = make_golden.inputs(name)
+    got = bi.batch_invariant_matmul(i["a"].cuda(), i["w"].cuda().T)
+    assert make_golden.raw(got).tobytes() == gold[f"{name}_mm"].tobytes()
+
+
+def test_fp32_configured_shape_tolerance_and_invariance(bi):
+    x, w = xw(256, 4096, 4096, torch.float32, 0)
+    xc, wc = x.cuda(), w.cuda()
+    full = bi.batch_invariant_matmul(xc, wc.T)
+    assert R.rel_err(R.matmul_f64(x[:8], w.T), full[:8]) < 1e-5
+    for M in (1, 4, 16, 64):
+        assert R.bits_of(bi.batch_invariant_matmul(xc[:M], wc.T)) == R.bits_of(full[:M])
+    assert R.bits_of(bi.batch_invariant_matmul(xc[255:], wc.T)) == R.bits_of(full[255:])
+
+
+# ---- tensor-core path ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (1, 4096, 4096), (4, 896, 896), (16, 4864, 896), (64, 4096, 4096),
+                                   (256, 4096, 4096), (130, 200, 520), (7, 136, 72), (300, 1000, 264)])
+def test_tensor_core_tolerance_and_split_equals_fused(bi, dt, M, N, K):
+    x, w = xw(M, N, K, dt, M * 3 + N + K)
+    xc, wc = x.cuda(), w.cuda()
+    auto = bi.batch_invariant_matmul(xc, wc.T)
+    assert R.rel_err(R.matmul_f64(x, w.T), auto) < TOL[dt]
+    split = bi.batch_invariant_matmul(xc, wc.T, path="split")
+    fused = bi.batch_invariant_matmul(xc, wc.T, path="fused")
+    assert R.bits_of(split) == R.bits_of(fused) == R.bits_of(auto)
+    bi.check_device_status()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_row_position_independence(bi, dt):
+    """The same activation row gives the same bits at every slot of the 128-row batch tile, in any
+    batch tile, next to any neighbours (the premise the whole contract rests on)."""
+    N, K = 512, 1024
+    x, w = xw(300, N, K, dt, 77)
+    wc = w.cuda()
+    probe = x[:1].cuda()
+    want = R.bits_of(bi.batch_invariant_matmul(probe, wc.T))
+    g = torch.Generator().manual_seed(5)
+    for pos in list(range(0, 128, 5)) + [127, 128, 129, 255, 256, 299]:
+        batch = torch.randn(300, K, generator=g).to(dt).cuda()
+        batch[pos] = probe[0]
+        for path in ("split", "fused"):
+            out = bi.batch_invariant_matmul(batch, wc.T, path=path)
+            assert R.bits_of(out[pos:pos + 1]) == want, (pos, path)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_strided_activation_and_leading_dims(bi, dt):
+    x, w = xw(24, 256, 512, dt, 3)
+    xc, wc = x.cuda(), w.cuda()
+    want = bi.batch_invariant_matmul(xc, wc.T)
+    big = torch.zeros(24, 512 + 24, dtype=dt, device="cuda")
+    big[:, 8:520] = xc
+    assert R.bits_of(bi.batch_invariant_matmul(big[:, 8:520], wc.T)) == R.bits_of(want)       # aligned pitch, in place
+    big[:, 3:515] = xc
+    assert R.bits_of(bi.batch_invariant_matmul(big[:, 3:515], wc.T)) == R.bits_of(want)       # misaligned -> copied
+    assert R.bits_of(bi.batch_invariant_matmul(xc.reshape(2, 3, 4, 512), wc.T).reshape(24, 256)) == R.bits_of(want)
+    mixed = bi.batch_invariant_matmul(xc.float(), wc.T)                                        # promoted to fp32
+    assert mixed.dtype == torch.float32
+
+
+# ---- quantized ------------------------------------------------------------------------------
+
+def quant_case(N, K, bits, gs, dt, seed):
+    g = torch.Generator().manual_seed(seed)
+    W = torch.randn(N, K, generator=g) * 0.02
+    return R.quantize_affine(W, group_size=gs, bits=bits, dtype=dt)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("bits,gs", [(4, 32), (4, 64), (4, 128), (8, 32), (8, 64), (8, 128)])
+def test_quantized_equals_dense_on_dequantized_weight(bi, dt, bits, gs):
+    N, K, M = 200, 1024, 9
+    p, s, b = quant_case(N, K, bits, gs, dt, bits * 100 + gs)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(M, K, generator=g).to(dt)
+    got = bi.batch_invariant_quantized_matmul(x.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=gs, bits=bits)
+    wd = R.dequant(p, s, b, group_size=gs, bits=bits, dtype=dt)            # oracle dequant, bit-exact spec
+    dense = bi.batch_invariant_matmul(x.cuda(), wd.cuda().T)
+    assert R.bits_of(got) == R.bits_of(dense)
+    assert R.rel_err(R.qmm_f64(x, p, s, b, group_size=gs, bits=bits), got) < TOL[dt]
+    for path in ("split", "fused"):
+        alt = bi.batch_invariant_quantized_matmul(x.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=gs, bits=bits, path=path)
+        assert R.bits_of(alt) == R.bits_of(got)
+    bi.check_device_status()
+
+
+@pytest.mark.parametrize("K,N", [(896, 896), (896, 4864), (4096, 4096), (4096, 14336)])
+def test_quantized_configured_shapes(bi, K, N):
+    dt = torch.bfloat16
+    p, s, b = quant_case(N, K, 4, 64, dt, K + N)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(64, K, generator=g).to(dt)
+    pc, sc, bc, xc = p.cuda(), s.cuda(), b.cuda(), x.cuda()
+    full = bi.batch_invariant_quantized_matmul(xc, pc, sc, bc, group_size=64, bits=4)
+    assert R.rel_err(R.qmm_f64(x[:4], p, s, b, group_size=64, bits=4), full[:4]) < 2e-2
+    for M in (1, 4, 16):
+        assert R.bits_of(bi.batch_invariant_quantized_matmul(xc[:M], pc, sc, bc, group_size=64, bits=4)) == R.bits_of(full[:M])
+    assert R.bits_of(bi.batch_invariant_quantized_matmul(xc[63:], pc, sc, bc, group_size=64, bits=4)) == R.bits_of(full[63:])
+    bi.check_device_status()
+
+
+def test_quantized_fp32_bit_exact_vs_oracle(bi):
+    """fp32 activations stage the dequantized weight in fp32 and take the CUDA-core order."""
+    p, s, b = quant_case(40, 256, 4, 64, torch.float32, 4)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 256, generator=g)
+    got = bi.batch_invariant_quantized_matmul(x.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=64, bits=4)
+    wd = R.dequant(p, s, b, group_size=64, bits=4, dtype=torch.float32)
+    assert R.bits_of(got) == R.bits_of(R.matmul_f32order(x, wd.T.contiguous()))
+
+
+def test_dequant_golden_fixture(bi):
+    """The kernel's dequantization, isolated: x = identity picks out single weight columns."""
+    gold = np.load(make_golden.OUT)
+    for bits in (4, 8):
+        p = torch.from_numpy(gold[f"q{bits}_codes"].copy())
+        g = torch.Generator().manual_seed(99)
+        W = torch.randn(8, 128, generator=g) * 0.02
+        p2, s, b = R.quantize_affine(W, group_size=32, bits=bits, dtype=torch.bfloat16)
+        assert torch.equal(p, p2)
+        eye = torch.eye(128, dtype=torch.bfloat16)
+        got = bi.batch_invariant_quantized_matmul(eye.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=32, bits=bits)
+        want = make_golden.unraw(gold[f"q{bits}_dequant"], torch.bfloat16)
+        assert torch.equal(got.cpu().T.contiguous(), want)

@@ -1,0 +1,59 @@
+"""RMSNorm on the GPU, through the C ABI, bit for bit against the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import reference as R
+from tests.golden import make_golden
+
+pytestmark = pytest.mark.gpu
+DTS = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("rows,D", [(1, 4096), (3, 4096), (256, 4096), (5, 100), (2, 8192), (4, 264), (2, 50000)])
+def test_bit_exact_vs_oracle(bi, dt, rows, D):
+    g = torch.Generator().manual_seed(rows * 131 + D)
+    x = (3 * torch.randn(rows, D, generator=g)).to(dt)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dt)
+    got = bi.batch_invariant_rms_norm(x.cuda(), w.cuda(), 1e-5)
+    assert R.bits_of(got) == R.bits_of(R.rms_norm(x, w, 1e-5))
+    got = bi.batch_invariant_rms_norm(x.cuda(), None, 1e-6)
+    assert R.bits_of(got) == R.bits_of(R.rms_norm(x, None, 1e-6))
+
+
+@pytest.mark.parametrize("dt", DTS)
+def test_leading_dims_and_unaligned_views(bi, dt):
+    g = torch.Generator().manual_seed(5)
+    x = (3 * torch.randn(2, 3, 257, generator=g)).to(dt)   # odd row length: the unstaged path
+    w = torch.randn(257, generator=g).to(dt)
+    got = bi.batch_invariant_rms_norm(x.cuda(), w.cuda(), 1e-5)
+    assert got.shape == x.shape
+    assert R.bits_of(got) == R.bits_of(R.rms_norm(x, w, 1e-5))
+    base = (3 * torch.randn(4, 4096 + 8, generator=g)).to(dt).cuda()
+    view = base[:, 3:4096 + 3]                            # misaligned rows -> wrapper copies
+    got = bi.batch_invariant_rms_norm(view, None, 1e-5)
+    assert R.bits_of(got) == R.bits_of(R.rms_norm(view.cpu(), None, 1e-5))
+
+
+@pytest.mark.parametrize("name", ["f32", "bf16", "f16"])
+def test_golden_fixture(bi, name):
+    gold = np.load(make_golden.OUT)
+    i = make_golden.inputs(name)
+    got = bi.batch_invariant_rms_norm(i["rms_x"].cuda(), i["rms_w"].cuda(), 1e-5)
+    assert make_golden.raw(got).tobytes() == gold[f"{name}_rms"].tobytes()
+
+
+@pytest.mark.parametrize("dt", DTS)
+def test_tolerance_vs_float64(bi, dt):
+    g = torch.Generator().manual_seed(0)
+    x = (3 * torch.randn(64, 4096, generator=g)).to(dt)
+    w = (1 + 0.1 * torch.randn(4096, generator=g)).to(dt)
+    got = bi.batch_invariant_rms_norm(x.cuda(), w.cuda(), 1e-5)
+    assert R.rel_err(R.rms_norm_f64(x, w, 1e-5), got) < (1e-5 if dt == torch.float32 else 2e-2)
+
+
+def test_empty(bi):
+    out = bi.batch_invariant_rms_norm(torch.empty(0, 64, device="cuda"), None, 1e-5)
+    assert out.shape == (0, 64)
