@@ -1,0 +1,217 @@
+"""Llama-3-architecture decoder over the batch-invariant ops, sharded without reductions.
+
+This is the whole-model caller the reference exercises through ``mlx_lm`` (harness/model_sweep.py:89-108
+and harness/generate_bench.py:24-33 there): prefill a batch of prompts, then greedy-decode with a KV
+cache, all linear / norm / attention math going through the four batch-invariant kernels.
+
+Sharding (R ranks, one process per GPU) uses only dimensions that need no cross-GPU reduction:
+  * every linear is column-parallel: rank r owns rows [r*N/R, (r+1)*N/R) of W[N, K] and produces
+    the matching slice of the output features;
+  * attention is sharded by KV head (each rank keeps the cache of its own heads);
+  * the feature slices are joined by all-gather (4 per layer + 1 for the logits).
+Each output element is produced on exactly one GPU by the same K order as on one GPU, so logits are
+bit-identical for every R and every batch size. RMSNorm, RoPE, residual adds, SwiGLU and argmax are
+replicated or elementwise.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import kernels as K
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    init_std: float = 0.02
+
+
+LLAMA3_8B = DecoderConfig()
+
+
+class KernelBackend:
+    """The four batch-invariant ops. Tests of the sharding logic swap in a CPU stand-in."""
+
+    def linear(self, x, w):                      # x[M, K] @ W[N, K]^T
+        return K.batch_invariant_matmul(x, w.T)
+
+    def qlinear(self, x, packed, group_size, bits):
+        p, s, b = packed
+        return K.batch_invariant_quantized_matmul(x, p, s, b, group_size=group_size, bits=bits)
+
+    def rms_norm(self, x, w, eps):
+        return K.batch_invariant_rms_norm(x, w, eps)
+
+    def prefill_attention(self, q, k, v, scale):
+        return K.batch_invariant_prefill_attention(q, k, v, scale=scale, causal=True)
+
+    def decode_attention(self, q, k, v, scale, kv_lens=None):
+        return K.batch_invariant_decode_attention(q, k, v, scale=scale, kv_lens=kv_lens)
+
+
+def _tensor_seed(seed: int, name: str) -> int:
+    return int.from_bytes(hashlib.blake2b(f"{seed}:{name}".encode(), digest_size=7).digest(), "little")
+
+
+def quantize_rows(W: torch.Tensor, group_size: int, bits: int):
+    """Affine per-group quantization of W[N, K] on its own device: scale = (max - min)/(2^bits - 1),
+    bias = min, code = round((w - bias)/scale) clipped, codes packed low to high in 32-bit words.
+    Row-wise, so quantizing a row shard equals the shard of the quantized matrix."""
+    N, Kd = W.shape
+    dt = W.dtype
+    g = W.float().reshape(N, Kd // group_size, group_size)
+    lo, hi = g.min(-1).values, g.max(-1).values
+    levels = float((1 << bits) - 1)
+    scale = ((hi - lo) / levels).clamp_min(1e-8).to(dt)
+    bias = lo.to(dt)
+    codes = torch.round((g - bias.float()[..., None]) / scale.float()[..., None]).clamp_(0, levels).to(torch.int64)
+    per = 32 // bits
+    shifts = torch.arange(per, device=W.device, dtype=torch.int64) * bits
+    words = (codes.reshape(N, Kd // per, per) << shifts).sum(-1)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    return words.contiguous(), scale.contiguous(), bias.contiguous()
+
+
+class ShardedDecoder:
+    def __init__(self, cfg: DecoderConfig, *, rank: int = 0, world: int = 1, device="cuda", dtype=torch.bfloat16,
+                 quant: tuple[int, int] | None = None, seed: int = 0, group=None, backend=None,
+                 max_batch: int = 64, max_len: int = 640):
+        if cfg.n_kv_heads % world or cfg.n_heads % world or cfg.ffn % world or cfg.d_model % world or cfg.vocab % world:
+            raise ValueError(f"world={world} must divide kv heads, heads, ffn, d_model and vocab")
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
+        self.dev, self.dt, self.quant, self.seed = torch.device(device), dtype, quant, seed
+        self.ops = backend or KernelBackend()
+        self.hq, self.hkv = cfg.n_heads // world, cfg.n_kv_heads // world
+        D = cfg.head_dim
+        self.layers = []
+        for li in range(cfg.n_layers):
+            wq = self._rows(f"l{li}.wq", cfg.n_heads * D, cfg.d_model, self.hq * D)
+            wk = self._rows(f"l{li}.wk", cfg.n_kv_heads * D, cfg.d_model, self.hkv * D)
+            wv = self._rows(f"l{li}.wv", cfg.n_kv_heads * D, cfg.d_model, self.hkv * D)
+            gate = self._rows(f"l{li}.gate", cfg.ffn, cfg.d_model, cfg.ffn // world)
+            up = self._rows(f"l{li}.up", cfg.ffn, cfg.d_model, cfg.ffn // world)
+            self.layers.append(dict(
+                qkv=self._pack(torch.cat([wq, wk, wv], 0)),
+                o=self._pack(self._rows(f"l{li}.wo", cfg.d_model, cfg.n_heads * D, cfg.d_model // world)),
+                gu=self._pack(torch.cat([gate, up], 0)),
+                down=self._pack(self._rows(f"l{li}.down", cfg.d_model, cfg.ffn, cfg.d_model // world)),
+                n1=self._norm(f"l{li}.n1"), n2=self._norm(f"l{li}.n2")))
+            del wq, wk, wv, gate, up
+        self.embed = self._full(f"embed", cfg.vocab, cfg.d_model)
+        self.head = self._pack(self._rows("lm_head", cfg.vocab, cfg.d_model, cfg.vocab // world))
+        self.nf = self._norm("final_norm")
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+        ang = torch.arange(max_len, dtype=torch.float64)[:, None] * inv[None, :]
+        self.cos = torch.cat([ang.cos(), ang.cos()], -1).float().to(self.dev)     # [max_len, D]
+        self.sin = torch.cat([ang.sin(), ang.sin()], -1).float().to(self.dev)
+        self.max_batch, self.max_len = max_batch, max_len
+        self.kc = [torch.zeros(max_batch, self.hkv, max_len, D, dtype=dtype, device=self.dev) for _ in range(cfg.n_layers)]
+        self.vc = [torch.zeros(max_batch, self.hkv, max_len, D, dtype=dtype, device=self.dev) for _ in range(cfg.n_layers)]
+        self.block_hook = None          # callable(layer_index, hidden[B, T, d]) -> None, for per-block hashing
+
+    # ---- weights: every tensor is drawn whole from its own seed, then sliced, so shards of any R agree
+    def _gen(self, name):
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(_tensor_seed(self.seed, name))
+        return g
+
+    def _full(self, name, n, k):
+        return (torch.randn(n, k, generator=self._gen(name), device=self.dev, dtype=torch.float32) * self.cfg.init_std).to(self.dt)
+
+    def _rows(self, name, n, k, rows_per_rank):
+        return self._full(name, n, k)[self.rank * rows_per_rank:(self.rank + 1) * rows_per_rank].contiguous()
+
+    def _norm(self, name):
+        return (1.0 + 0.1 * torch.randn(self.cfg.d_model, generator=self._gen(name), device=self.dev, dtype=torch.float32)).to(self.dt)
+
+    def _pack(self, w):
+        if self.quant is None:
+            return w
+        bits, gs = self.quant
+        return quantize_rows(w, gs, bits)
+
+    def _lin(self, x, w):
+        if self.quant is None:
+            return self.ops.linear(x, w)
+        return self.ops.qlinear(x, w, self.quant[1], self.quant[0])
+
+    # ---- collectives: join feature slices [M, F/R] -> [M, F], rank-major (the unsharded order)
+    def _gather(self, local):
+        if self.world == 1:
+            return local
+        import torch.distributed as dist
+        M, f = local.shape
+        buf = torch.empty(self.world, M, f, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)
+        return buf.permute(1, 0, 2).reshape(M, self.world * f)
+
+    def _rope(self, x, pos):                       # x[B, H, T, D], pos[T] (long, device)
+        cos, sin = self.cos[pos][None, None], self.sin[pos][None, None]
+        xf = x.float()
+        half = x.shape[-1] // 2
+        rot = torch.cat([-xf[..., half:], xf[..., :half]], -1)
+        return (xf * cos + rot * sin).to(x.dtype)
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, start: int) -> torch.Tensor:
+        """tokens[B, T] continue every sequence at position `start`; returns logits [B, vocab] of the
+        last position. T > 1 is a prefill (causal over cache + new keys), T == 1 a decode step."""
+        cfg, D = self.cfg, self.cfg.head_dim
+        B, T = tokens.shape
+        M = B * T
+        end = start + T
+        pos = torch.arange(start, end, device=self.dev)
+        x = self.embed[tokens.reshape(-1)]                                     # [M, d]
+        scale = 1.0 / math.sqrt(D)
+        for li, L in enumerate(self.layers):
+            h = self.ops.rms_norm(x, L["n1"], cfg.eps)
+            qkv = self._lin(h, L["qkv"]).reshape(B, T, self.hq + 2 * self.hkv, D).transpose(1, 2)
+            q = self._rope(qkv[:, :self.hq], pos)
+            k = self._rope(qkv[:, self.hq:self.hq + self.hkv], pos)
+            v = qkv[:, self.hq + self.hkv:]
+            self.kc[li][:B, :, start:end] = k
+            self.vc[li][:B, :, start:end] = v
+            kk, vv = self.kc[li][:B, :, :end], self.vc[li][:B, :, :end]
+            if T == 1:
+                a = self.ops.decode_attention(q.contiguous(), kk, vv, scale)
+            else:
+                a = self.ops.prefill_attention(q.contiguous(), kk, vv, scale)
+            a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
+            x = x + self._gather(self._lin(a, L["o"]))
+            h = self.ops.rms_norm(x, L["n2"], cfg.eps)
+            gu = self._lin(h, L["gu"])
+            f = cfg.ffn // self.world
+            act = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+            x = x + self._gather(self._lin(self._gather(act), L["down"]))
+            if self.block_hook is not None:
+                self.block_hook(li, x.reshape(B, T, -1))
+        last = x.reshape(B, T, -1)[:, -1]
+        h = self.ops.rms_norm(last.contiguous(), self.nf, cfg.eps)
+        return self._gather(self._lin(h, self.head))
+
+
+@torch.no_grad()
+def greedy_generate(model: ShardedDecoder, prompts: torch.Tensor, steps: int):
+    """Prefill `prompts` [B, P], then `steps` greedy tokens. Returns (tokens [B, steps], last logits)."""
+    B, P = prompts.shape
+    logits = model.forward(prompts, 0)
+    out = []
+    for s in range(steps):
+        nxt = logits.argmax(-1)
+        out.append(nxt)
+        if s + 1 < steps:
+            logits = model.forward(nxt[:, None], P + s)
+    return torch.stack(out, 1), logits

@@ -32,14 +32,15 @@ def test_mode_routes_torch_modules(bi):
     kv = torch.randn(2, 2, 5, 64, device="cuda", dtype=torch.bfloat16)
     bi.reset_stats()
     with bi.set_batch_invariant_mode(strict=True):
-        y = lin(norm(x))
-        z = x @ lin.weight.T
+        h = norm(x)
+        y = lin(h)
+        z = h @ lin.weight.T
         a = F.scaled_dot_product_attention(q, kv, kv, is_causal=True, enable_gqa=True)
         d = F.scaled_dot_product_attention(q[:, :, -1:], kv, kv, enable_gqa=True)
     st = bi.stats()
     assert st["fallbacks"] == {}
     assert st["handled"] == {"rms_norm": 1, "addmm": 1, "matmul": 1, "sdpa_prefill": 1, "sdpa_decode": 1}
-    assert torch.equal(y, z + lin.bias)
+    assert torch.equal(y, z + lin.bias)            # addmm adds the bias after the product is rounded
     assert torch.equal(a[:, :, -1:], d)
     ref = F.scaled_dot_product_attention(q, kv, kv, is_causal=True, enable_gqa=True)
     assert (a.float() - ref.float()).abs().max() < 3e-2
