@@ -154,9 +154,9 @@ class ShardedDecoder:
             return local
         import torch.distributed as dist
         M, f = local.shape
-        buf = torch.empty(self.world, M, f, dtype=local.dtype, device=local.device)
+        buf = torch.empty(self.world * M, f, dtype=local.dtype, device=local.device)
         dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)
-        return buf.permute(1, 0, 2).reshape(M, self.world * f)
+        return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
     def _rope(self, x, pos):                       # x[B, H, T, D], pos[T] (long, device)
         cos, sin = self.cos[pos][None, None], self.sin[pos][None, None]

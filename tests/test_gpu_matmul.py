@@ -173,3 +173,30 @@ def test_dequant_golden_fixture(bi):
         got = bi.batch_invariant_quantized_matmul(eye.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=32, bits=bits)
         want = make_golden.unraw(gold[f"q{bits}_dequant"], torch.bfloat16)
         assert torch.equal(got.cpu().T.contiguous(), want)
+
+
+# ---- weight-row position independence (what sharding a weight by rows relies on) ----------------
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_weight_row_position_independence(bi, dt):
+    """Rows [o, o+n) of W used as a weight of their own give the same bits as columns [o, o+n) of the
+    full product: an output's bits do not depend on which tile, or which row of the 128-row weight
+    tile, its weight row sits in. Column-parallel sharding over GPUs changes exactly that."""
+    x, w = xw(40, 1024, 768, dt, 21)
+    xc, wc = x.cuda(), w.cuda()
+    full = bi.batch_invariant_matmul(xc, wc.T)
+    for off, n in [(0, 512), (512, 512), (128, 256), (8, 120), (1016, 8), (56, 200)]:
+        part = bi.batch_invariant_matmul(xc, wc[off:off + n].T)
+        assert R.bits_of(part) == R.bits_of(full[:, off:off + n].contiguous()), (off, n)
+
+
+def test_quantized_weight_row_position_independence(bi):
+    dt = torch.bfloat16
+    p, s, b = quant_case(768, 1024, 4, 64, dt, 33)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(12, 1024, generator=g).to(dt).cuda()
+    pc, sc, bc = p.cuda(), s.cuda(), b.cuda()
+    full = bi.batch_invariant_quantized_matmul(x, pc, sc, bc, group_size=64, bits=4)
+    for off, n in [(0, 384), (384, 384), (128, 128), (40, 200)]:
+        part = bi.batch_invariant_quantized_matmul(x, pc[off:off + n], sc[off:off + n], bc[off:off + n], group_size=64, bits=4)
+        assert R.bits_of(part) == R.bits_of(full[:, off:off + n].contiguous()), (off, n)
