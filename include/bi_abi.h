@@ -2,9 +2,10 @@
  * C ABI of the B200 batch-invariant kernel library (libbi_b200.so).
  *
  * Every entry point is a plain C function over raw device pointers, sizes and
- * element strides. The library owns no device memory: inputs, outputs and any
- * scratch ("workspace") are allocated by the caller; the matching
- * *_workspace_bytes() call says how much scratch an op needs. Launches go to
+ * element strides. The library owns no device memory (one documented exception:
+ * bi_attn_decode_static): inputs, outputs and any scratch ("workspace") are
+ * allocated by the caller; the matching *_workspace_bytes() call says how much
+ * scratch an op needs. Launches go to
  * the caller's stream and never synchronise. The return value is a bi_status;
  * bi_last_error() gives a thread-local message for the last non-zero status.
  * Nothing throws or aborts across this boundary.
@@ -109,6 +110,27 @@ int bi_attn_decode(const void* q, const void* k, const void* v, void* out, const
                    void* workspace, size_t workspace_bytes, int64_t B, int64_t Hq, int64_t Hkv,
                    int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh, int64_t kv_sl, float scale,
                    int split_size, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Decode attention without a caller workspace. No counterpart in the         *
+ * reference: there the MLX runtime allocates every kernel output and         *
+ * intermediate. Same inputs, outputs and arithmetic as bi_attn_decode; the   *
+ * per-split partials live in an array built into the library                 *
+ * (BI_ATTN_DECODE_STATIC_MAX_BYTES per GPU, held until the process exits),    *
+ * so the call allocates nothing. Meant for hosts that cannot allocate on the  *
+ * library's behalf: a plugin inside a runtime that exposes no allocator to C, *
+ * or a server that has already reserved HBM for its own pool. Problems whose  *
+ * partials (bi_attn_decode_workspace_bytes) exceed the limit return           *
+ * BI_ERR_WORKSPACE. All calls on a device share the array: calls that may     *
+ * overlap on the GPU race and must be ordered by the caller. The first call   *
+ * on each device resolves the array's address; issue it at start-up, before   *
+ * any stream capture on that device.                                          *
+ * ------------------------------------------------------------------------ */
+#define BI_ATTN_DECODE_STATIC_MAX_BYTES (8u << 20)
+
+int bi_attn_decode_static(const void* q, const void* k, const void* v, void* out, const int32_t* kv_lens,
+                          int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh,
+                          int64_t kv_sl, float scale, int split_size, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Prefill attention (any number of queries, right-aligned to the cache end  *
