@@ -157,6 +157,18 @@ class MatmulBF16(Workload):
         return 2.0 * rows * self.N * self.K / dt / 1e12, f"first {rows} of {self.M} rows, all {self.N} columns, {dt:.1f} s"
 
 
+class MatmulBF16M1(MatmulBF16):
+    name, M = "matmul_bf16_m1", 1
+
+    def __init__(self, torch, bi, dev):
+        super().__init__(torch, bi, dev)
+        self.launches_per_step = 2                        # split kernel + combine
+
+
+class MatmulBF16M64(MatmulBF16M1):
+    name, M = "matmul_bf16_m64", 64
+
+
 class QMM4Decode(Workload):
     name, metric, unit, dtype = "qmm4_decode", "4-bit decode HBM GB/s", "GB/s", "bf16"
     M, N, K, gs, bits = 1, 14336, 4096, 64, 4
@@ -286,7 +298,7 @@ class RMSNormW(Workload):
         return self.algo_bytes() / dt / 1e9, f"whole [{self.M},{self.D}] input, mean of {reps} passes"
 
 
-WORKLOADS = {c.name: c for c in (MatmulBF16, QMM4Decode, AttnDecode, RMSNormW)}
+WORKLOADS = {c.name: c for c in (MatmulBF16, MatmulBF16M1, MatmulBF16M64, QMM4Decode, AttnDecode, RMSNormW)}
 
 
 # ---------------------------------------------------------------------------------------------

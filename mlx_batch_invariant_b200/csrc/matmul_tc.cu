@@ -24,11 +24,13 @@
 // Both are one persistent kernel: CTA c takes a contiguous range of units, a
 // TMA warp streams stages through a ring of shared-memory buffers, one thread
 // issues the MMAs into one of two TMEM accumulators, four epilogue warps drain
-// the other. For affine-quantized weights the TMA warp brings the packed codes
-// instead and four more warps turn them into the same swizzled 16-bit tile the
-// dense path would have loaded (fma(float(code), scale, bias) in fp32, one
-// rounding -- mlx_batch_invariant/kernels/quantized.py:44-67), so the MMA
-// sequence is the dense one.
+// the other (the fused path keeps its running total in a third TMEM region).
+// For affine-quantized weights the TMA ring carries the packed codes (a deep
+// ring of small stages, so enough bytes are in flight to cover HBM latency)
+// and eight more warps turn them into the same swizzled 16-bit tile the dense
+// path would have loaded, in a short second ring (fma(float(code), scale, bias)
+// in fp32, one rounding -- mlx_batch_invariant/kernels/quantized.py:44-67), so
+// the MMA sequence is the dense one.
 //
 // Every wait on a shared-memory barrier is bounded in time; a wait that runs
 // out records a code in the caller's status word, raises a CTA-wide abort flag
@@ -47,21 +49,33 @@ constexpr int BLOCK_M = 128;  // batch rows per tile   (UMMA N)
 constexpr int BLOCK_K = 64;   // elements per stage along K: 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BLOCK_N * BLOCK_K * 2;
-constexpr int X_TILE_BYTES = BLOCK_M * BLOCK_K * 2;
-constexpr int TMEM_COLS = 2 * BLOCK_M;  // two accumulators
+constexpr int TMEM_ACC1 = BLOCK_M;       // second accumulator
+constexpr int TMEM_TOTAL = 2 * BLOCK_M;  // running total of the fused path
+constexpr int TMEM_COLS = 512;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+#ifndef BI_EPI_SLEEP_NS
+#define BI_EPI_SLEEP_NS 100
+#endif
 
+constexpr int MAX_SLOTS = 8;     // ring depths and the chunk-completion barrier array (power of two)
 constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EPI0 = 2, WARP_DEQ0 = 6;
+constexpr int N_DEQ_WARPS = 8;
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int BAR_BYTES = 512;
 
 template <int QBITS> struct Cfg {
     static constexpr int RAW_BYTES = QBITS ? BLOCK_N * BLOCK_K * QBITS / 8 : 0;
-    static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES + RAW_BYTES;
-    static constexpr int STAGES = QBITS ? 5 : 6;
-    static constexpr int THREADS = QBITS ? 320 : 192;
-    static constexpr int BAR_BYTES = 512;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+    static constexpr int THREADS = QBITS ? 32 * (WARP_DEQ0 + N_DEQ_WARPS) : 192;
 };
 
+// Shared memory, in this order (every tile 1024-byte aligned):
+//   x ring     load_slots x ks x x_bytes  activation tiles (TMA, 128-byte swizzle). Only the batch rows
+//                                         that exist are loaded; the MMA still reads 128 rows from the
+//                                         tile base, so the ring sits first and what follows it is
+//                                         valid (unread-result) memory.
+//   W ring     dense: load_slots x ks x 16 KB (TMA)   quantized: w_slots x ks x 16 KB (dequantizers)
+//   raw ring   quantized only: load_slots x ks x RAW_BYTES packed codes (TMA, no swizzle)
+//   barriers
 struct Params {
     void* out;          // [M, N] in T (fused)
     float* part;        // [G, M, N] fp32 (split)
@@ -72,6 +86,11 @@ struct Params {
     int n_tiles, m_tiles;
     int split;          // 1: split jobs, 0: fused units
     int x_rows;         // rows of the activation TMA box
+    int x_bytes;        // shared-memory bytes reserved per activation tile
+    int ks;             // K steps (of 64) per chunk = per ring slot = per tcgen05.commit
+    int load_slots;     // depth of the TMA ring, in chunks
+    int w_slots;        // depth of the dequantized-weight ring (quantized), in chunks
+    int w_ring_slots;   // slots of the ring the MMA reads weights from (w_slots, or load_slots when dense)
     int gs;
     long long units;
 };
@@ -81,18 +100,42 @@ enum { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_EPI = 3, ROLE_DEQ = 4 };
 struct Ctl {
     int32_t* status;
     volatile int* abort_flag;  // shared memory
+#ifdef BI_TC_PROFILE
+    long long* waited;         // cycles this thread spent in wait_bounded
+#endif
 };
 
 __device__ __forceinline__ void report(const Ctl& c, int role, int idx) {
     *c.abort_flag = 1;
+#ifndef BI_TC_PROFILE
     if (c.status) atomicCAS(c.status, 0, (int)(0x10000 | (role << 8) | (idx & 0xff)));
+#endif
 }
 
 // Wait for barrier phase `parity` to complete. Gives up after WAIT_LIMIT_NS or when another
 // role has raised the abort flag; returns false then.
+__device__ __forceinline__ bool wait_bounded_impl(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx);
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx) {
-    for (int i = 0; i < 4096; ++i)
-        if (ptx::mbar_try_wait(bar, parity)) return true;
+#ifdef BI_TC_PROFILE
+    const long long t0 = clock64();
+    const bool ok = wait_bounded_impl(bar, parity, c, role, idx);
+    *c.waited += clock64() - t0;
+    return ok;
+#else
+    return wait_bounded_impl(bar, parity, c, role, idx);
+#endif
+}
+__device__ __forceinline__ bool wait_bounded_impl(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx) {
+    if (role == ROLE_EPI || role == ROLE_DEQ) {
+        // whole warps wait here; back off so they do not take issue slots from the TMA and MMA threads
+        for (int i = 0; i < 2048; ++i) {
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+            __nanosleep(BI_EPI_SLEEP_NS);
+        }
+    } else {
+        for (int i = 0; i < 4096; ++i)
+            if (ptx::mbar_try_wait(bar, parity)) return true;
+    }
     const uint64_t t0 = ptx::globaltimer_ns();
     while (true) {
         for (int i = 0; i < 256; ++i)
@@ -100,24 +143,6 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, cons
         if (*c.abort_flag) return false;
         if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) { report(c, role, idx); return false; }
     }
-}
-
-struct Unit {
-    int n0, m0, g0, g1;
-};
-__device__ __forceinline__ Unit decode_unit(const Params& p, long long u) {
-    Unit r;
-    long long tile;
-    if (p.split) { tile = u / p.G; r.g0 = (int)(u % p.G); r.g1 = r.g0 + 1; }
-    else         { tile = u; r.g0 = 0; r.g1 = p.G; }
-    r.n0 = (int)(tile / p.m_tiles) * BLOCK_N;
-    r.m0 = (int)(tile % p.m_tiles) * BLOCK_M;
-    return r;
-}
-__device__ __forceinline__ int stages_in_group(const Params& p, int g) {
-    const int kg0 = g * GROUP_K;
-    const int kg1 = min(p.K, kg0 + GROUP_K);
-    return (kg1 - kg0 + BLOCK_K - 1) / BLOCK_K;
 }
 
 template <typename T> struct Pack2;
@@ -134,59 +159,144 @@ template <> struct Pack2<__half> {
     }
 };
 
-// Eight consecutive codes -> eight T values packed for one 16-byte swizzle chunk.
+// Eight consecutive codes -> eight T values, one 16-byte swizzle chunk.
+//   value = T(fma(float(code), scale, bias))   fp32 fma, one rounding.
+// float(code) is formed exactly without an integer->float conversion: a byte permute drops the code
+// into the low mantissa byte of 2^23 (0x4B0000cc = 8388608 + cc) and 2^23 is subtracted, which is
+// exact. The subtract and the fma run as packed f32x2 instructions: two independent IEEE
+// round-to-nearest operations each, same bits as the scalar forms.
 template <typename T, int QBITS>
-__device__ __forceinline__ uint4 dequant8(const uint32_t* words, float s, float b) {
-    float f[8];
+__device__ __forceinline__ uint4 dequant8(const uint32_t* words, uint64_t s2, uint64_t b2) {
+    const uint64_t neg_magic = ptx::pack2(-8388608.0f, -8388608.0f);
+    uint32_t src_even[4], src_odd[4];  // register + byte index holding codes 2i and 2i+1
+    uint32_t o[4];
     if (QBITS == 4) {
-        const uint32_t w = words[0];
+        const uint32_t lo = words[0] & 0x0F0F0F0Fu;          // bytes: codes 0, 2, 4, 6
+        const uint32_t hi = (words[0] >> 4) & 0x0F0F0F0Fu;   // bytes: codes 1, 3, 5, 7
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fma_rn((float)((w >> (4 * i)) & 0xFu), s, b);
+        for (int i = 0; i < 4; ++i) {
+            src_even[i] = __byte_perm(lo, 0x4B000000u, 0x7540u + i);
+            src_odd[i] = __byte_perm(hi, 0x4B000000u, 0x7540u + i);
+        }
     } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fma_rn((float)((words[i >> 2] >> (8 * (i & 3))) & 0xFFu), s, b);
+        for (int i = 0; i < 4; ++i) {
+            src_even[i] = __byte_perm(words[i >> 1], 0x4B000000u, 0x7540u + 2 * (i & 1));
+            src_odd[i] = __byte_perm(words[i >> 1], 0x4B000000u, 0x7540u + 2 * (i & 1) + 1);
+        }
     }
-    uint4 o;
-    o.x = Pack2<T>::rn(f[0], f[1]); o.y = Pack2<T>::rn(f[2], f[3]);
-    o.z = Pack2<T>::rn(f[4], f[5]); o.w = Pack2<T>::rn(f[6], f[7]);
-    return o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint64_t v = ptx::pack2(__uint_as_float(src_even[i]), __uint_as_float(src_odd[i]));
+        v = ptx::add2_rn(v, neg_magic);
+        v = ptx::fma2_rn(v, s2, b2);
+        float x, y;
+        ptx::unpack2(v, x, y);
+        o[i] = Pack2<T>::rn(x, y);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
 }
+
+// Work is cut into "chunks": up to p.ks consecutive 64-wide K steps of one K group. A chunk is the
+// unit of every ring slot and of MMA completion tracking: the issuing thread commits once per chunk
+// (a tcgen05.commit drains the tensor pipe for ~200 cycles, so it is issued as rarely as the
+// shared-memory budget allows), and everyone who needs "the MMAs of chunk c are done" -- the TMA
+// thread before it refills a slot, the dequantizers before they overwrite a weight slot, the
+// epilogue before it reads an accumulator -- waits on the same barrier done[c % 8].
+struct ChunkIter {
+    // Enumerates (unit, group, chunk) in the one order every role follows, and keeps the ring
+    // positions of the current chunk. Only the constructor divides; stepping is increments.
+    const Params& p;
+    int left;                 // units still to go, including the current one
+    int nt, mt;               // weight tile, batch tile of the current unit
+    int g, g1;                // current K group, end of the unit's group range
+    int nst, c, nchunk;       // K steps in the group, chunk index, chunks in the group
+    int ci;                   // CTA-local running chunk index
+    int l, w, d;              // load slot, weight slot, completion barrier of the chunk
+    uint32_t lph, wph, dph;   // phase parities of those rings
+    __device__ __forceinline__ ChunkIter(const Params& pp, int ub, int ue) : p(pp), left(ue - ub) {
+        ci = 0; l = w = d = 0; lph = wph = dph = 0;
+        if (left <= 0) return;
+        int tile;
+        if (p.split) { tile = ub / p.G; g = ub - tile * p.G; g1 = g + 1; }
+        else         { tile = ub; g = 0; g1 = p.G; }
+        nt = tile / p.m_tiles; mt = tile - nt * p.m_tiles;
+        start_group();
+    }
+    __device__ __forceinline__ void start_group() {
+        const int kw = min(p.K - g * GROUP_K, GROUP_K);
+        nst = (kw + BLOCK_K - 1) / BLOCK_K;
+        nchunk = p.ks == 4 ? 1 : (nst + p.ks - 1) / p.ks;
+        c = 0;
+    }
+    __device__ __forceinline__ bool valid() const { return left > 0; }
+    __device__ __forceinline__ int n0() const { return nt * BLOCK_N; }
+    __device__ __forceinline__ int m0() const { return mt * BLOCK_M; }
+    __device__ __forceinline__ int ksteps() const { return min(p.ks, nst - c * p.ks); }
+    __device__ __forceinline__ int k0() const { return g * GROUP_K + c * p.ks * BLOCK_K; }
+    __device__ __forceinline__ bool first_in_group() const { return c == 0; }
+    __device__ __forceinline__ bool last_in_group() const { return c == nchunk - 1; }
+    __device__ __forceinline__ void next() {
+        ++ci;
+        if (++l == p.load_slots) { l = 0; lph ^= 1u; }
+        if (++w == p.w_ring_slots) { w = 0; wph ^= 1u; }
+        if (++d == MAX_SLOTS) { d = 0; dph ^= 1u; }
+        if (++c < nchunk) return;
+        if (++g < g1) { start_group(); return; }
+        if (--left <= 0) return;
+        if (p.split) {
+            if (g == p.G) { g = 0; if (++mt == p.m_tiles) { mt = 0; ++nt; } }
+            g1 = g + 1;
+        } else {
+            g = 0;
+            if (++mt == p.m_tiles) { mt = 0; ++nt; }
+        }
+        start_group();
+    }
+};
 
 template <typename T, int QBITS>
 __global__ void __launch_bounds__(Cfg<QBITS>::THREADS, 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const Params p) {
     using C = Cfg<QBITS>;
-    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    // stage s: [W tile 16 KB | X tile 16 KB | raw codes]
-    auto w_tile = [&](int s) { return smem_base + (uint32_t)s * C::STAGE_BYTES; };
-    auto x_tile = [&](int s) { return w_tile(s) + W_TILE_BYTES; };
-    auto raw_tile = [&](int s) { return x_tile(s) + X_TILE_BYTES; };
-    const uint32_t bar_base = smem_base + STAGES * C::STAGE_BYTES;
-    auto bar_full = [&](int s) { return bar_base + 8u * s; };                  // operands ready for the MMA
-    auto bar_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };      // stage free again
-    auto bar_raw = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };    // TMA landed (quantized)
-    auto bar_tfull = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };  // accumulator complete
-    auto bar_tempty = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
-    uint8_t* misc = smem_gen + STAGES * C::STAGE_BYTES + 8 * (3 * STAGES + 4);
+    const int LS = p.load_slots, KS = p.ks;
+    const int WS = QBITS ? p.w_slots : p.load_slots;
+    const uint32_t w_ring = smem_base + (uint32_t)(LS * KS) * p.x_bytes;
+    const uint32_t raw_ring = w_ring + (uint32_t)(WS * KS) * W_TILE_BYTES;
+    const uint32_t bar_base = raw_ring + (uint32_t)(LS * KS) * C::RAW_BYTES;
+    auto x_tile = [&](int l, int j) { return smem_base + (uint32_t)(l * KS + j) * p.x_bytes; };
+    auto w_tile = [&](int w, int j) { return w_ring + (uint32_t)(w * KS + j) * W_TILE_BYTES; };
+    auto raw_tile = [&](int l, int j) { return raw_ring + (uint32_t)(l * KS + j) * C::RAW_BYTES; };
+    auto bar_lfull = [&](int l) { return bar_base + 8u * l; };                    // TMA landed (slot l)
+    auto bar_wfull = [&](int w) { return bar_base + 8u * (MAX_SLOTS + w); };      // dequantized chunk ready
+    auto bar_done = [&](int d) { return bar_base + 8u * (2 * MAX_SLOTS + d); };   // MMAs of a chunk complete
+    auto bar_tempty = [&](int b) { return bar_base + 8u * (3 * MAX_SLOTS + b); }; // accumulator drained
+    uint8_t* misc = smem_gen + (bar_base - smem_base) + 8 * (3 * MAX_SLOTS + 2);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef BI_TC_PROFILE
+    long long waited = 0;
+    const long long t_start = clock64();
+    const Ctl ctl{p.status, abort_flag, &waited};
+#else
     const Ctl ctl{p.status, abort_flag};
+#endif
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(bar_full(s), QBITS ? 4 : 1);
-            ptx::mbar_init(bar_empty(s), 1);
-            ptx::mbar_init(bar_raw(s), 1);
+        for (int i = 0; i < MAX_SLOTS; ++i) {
+            ptx::mbar_init(bar_lfull(i), 1);
+            ptx::mbar_init(bar_wfull(i), N_DEQ_WARPS);
+            ptx::mbar_init(bar_done(i), 1);
         }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(bar_tfull(b), 1); ptx::mbar_init(bar_tempty(b), 4); }
+        for (int b = 0; b < 2; ++b) ptx::mbar_init(bar_tempty(b), 4);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_w);
         ptx::prefetch_tensormap(&tmap_x);
@@ -200,40 +310,41 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long ub = p.units * blockIdx.x / gridDim.x;
-    const long long ue = p.units * (blockIdx.x + 1) / gridDim.x;
+    const int ub = (int)(p.units * blockIdx.x / gridDim.x);
+    const int ue = (int)(p.units * (blockIdx.x + 1) / gridDim.x);
+    // wait until the MMAs of chunk `ci` (CTA-local running index) have completed
+    auto wait_done = [&](int ci, int role) {   // MAX_SLOTS is a power of two: mask and shift, no division
+        return wait_bounded(bar_done(ci & (MAX_SLOTS - 1)), (uint32_t)(ci >> 3) & 1u, ctl, role, 16 + (ci & (MAX_SLOTS - 1)));
+    };
+    static_assert(MAX_SLOTS == 8, "wait_done shifts by log2(MAX_SLOTS)");
 
     if (warp == WARP_TMA) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const uint32_t tx_bytes = (uint32_t)p.x_rows * BLOCK_K * 2 + (QBITS ? C::RAW_BYTES : W_TILE_BYTES);
-            int s = 0; uint32_t ph = 0; long long issued = 0; bool ok = true;
-            for (long long u = ub; u < ue && ok; ++u) {
-                const Unit un = decode_unit(p, u);
-                for (int g = un.g0; g < un.g1 && ok; ++g) {
-                    const int nst = stages_in_group(p, g);
-                    for (int ks = 0; ks < nst; ++ks) {
-                        if (!wait_bounded(bar_empty(s), ph ^ 1u, ctl, ROLE_TMA, s)) { ok = false; break; }
-                        const int k0 = g * GROUP_K + ks * BLOCK_K;
-                        const uint32_t bar = QBITS ? bar_raw(s) : bar_full(s);
-                        ptx::mbar_expect_tx(bar, tx_bytes);
-                        if (QBITS) ptx::tma_load_2d(raw_tile(s), &tmap_w, k0 * QBITS / 32, un.n0, bar);
-                        else       ptx::tma_load_2d(w_tile(s), &tmap_w, k0, un.n0, bar);
-                        ptx::tma_load_2d(x_tile(s), &tmap_x, k0, un.m0, bar);
-                        ++issued;
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
-                    }
+            const uint32_t step_bytes = (uint32_t)p.x_rows * BLOCK_K * 2 + (QBITS ? C::RAW_BYTES : W_TILE_BYTES);
+            bool ok = true;
+            ChunkIter it(p, ub, ue);
+            for (; it.valid() && ok; it.next()) {
+                const int l = it.l;
+                if (it.ci >= LS && !wait_done(it.ci - LS, ROLE_TMA)) { ok = false; break; }
+                const int kc = it.ksteps();
+                const uint32_t bar = bar_lfull(l);
+                ptx::mbar_expect_tx(bar, step_bytes * kc);
+                const int n0 = it.n0(), m0 = it.m0();
+                for (int j = 0; j < kc; ++j) {
+                    const int k0 = it.k0() + j * BLOCK_K;
+                    if (QBITS) ptx::tma_load_2d(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar);
+                    else       ptx::tma_load_2d(w_tile(l, j), &tmap_w, k0, n0, bar);
+                    ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
                 }
             }
             if (!ok) {
                 // Let the copies already in flight land before the CTA goes away.
-                const long long n = issued < STAGES ? issued : STAGES;
-                for (long long i = 0; i < n; ++i) {
-                    int si = s - 1 - (int)i; uint32_t pi = ph;
-                    if (si < 0) { si += STAGES; pi ^= 1u; }
-                    const uint32_t bar = QBITS ? bar_raw(si) : bar_full(si);
+                const int ci = it.ci;
+                for (int cj = max(0, ci - LS); cj < ci; ++cj) {
                     const uint64_t t0 = ptx::globaltimer_ns();
-                    while (!ptx::mbar_try_wait(bar, pi) && ptx::globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
+                    while (!ptx::mbar_try_wait(bar_lfull(cj % LS), (uint32_t)(cj / LS) & 1u) &&
+                           ptx::globaltimer_ns() - t0 < WAIT_LIMIT_NS) {}
                 }
             }
         }
@@ -243,136 +354,200 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BLOCK_M >> 3) << 17) |
                                        ((uint32_t)(BLOCK_N >> 4) << 24);
-            int s = 0; uint32_t ph = 0; long long job = 0; bool ok = true;
-            for (long long u = ub; u < ue && ok; ++u) {
-                const Unit un = decode_unit(p, u);
-                for (int g = un.g0; g < un.g1 && ok; ++g, ++job) {
-                    const int buf = (int)(job & 1);
-                    if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 16 + buf)) { ok = false; break; }
-                    ptx::tc_fence_after();
-                    const uint32_t tmem_d = tmem_base + (uint32_t)buf * BLOCK_M;
-                    const int kg0 = g * GROUP_K;
-                    const int kg1 = min(p.K, kg0 + GROUP_K);
-                    const int nst = stages_in_group(p, g);
-                    for (int ks = 0; ks < nst; ++ks) {
-                        if (!wait_bounded(bar_full(s), ph, ctl, ROLE_MMA, s)) { ok = false; break; }
-                        ptx::tc_fence_after();
-                        const int kleft = kg1 - (kg0 + ks * BLOCK_K);
-                        const int nsteps = (min(kleft, BLOCK_K) + UMMA_K - 1) / UMMA_K;
-                        for (int kk = 0; kk < nsteps; ++kk) {
-                            const uint64_t da = ptx::smem_desc_sw128(w_tile(s) + kk * UMMA_K * 2);
-                            const uint64_t db = ptx::smem_desc_sw128(x_tile(s) + kk * UMMA_K * 2);
-                            ptx::umma_f16(tmem_d, da, db, IDESC, (ks | kk) ? 1u : 0u);
-                        }
-                        ptx::umma_commit(bar_empty(s));
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
-                    }
-                    if (ok) ptx::umma_commit(bar_tfull(buf));
+            int job = -1; bool ok = true;
+            uint32_t tmem_d = tmem_base;
+#ifdef BI_TC_PROFILE
+            long long prof_fence = 0, prof_mma = 0, prof_commit = 0;
+#endif
+            for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
+                if (it.first_in_group()) {
+                    ++job;
+                    const int buf = job & 1;
+                    if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
+                    tmem_d = tmem_base + (uint32_t)buf * TMEM_ACC1;
                 }
+                const int l = it.l, w = it.w;
+                const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
+                if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
+#ifdef BI_TC_PROFILE
+                const long long tq0 = clock64();
+#endif
+                ptx::tc_fence_after();
+#ifdef BI_TC_PROFILE
+                const long long tq1 = clock64();
+#endif
+                const int kc = it.ksteps();
+                const int kend = min(p.K, (it.g + 1) * GROUP_K);
+                for (int j = 0; j < kc; ++j) {
+                    const int kleft = kend - (it.k0() + j * BLOCK_K);
+                    // one descriptor per operand and K step of 64; a UMMA K step of 16 elements is
+                    // +32 bytes, i.e. +2 in the descriptor's 16-byte address field
+                    const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
+                    const uint64_t db = ptx::smem_desc_sw128(x_tile(l, j));
+                    if (kleft >= BLOCK_K) {
+                        if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
+                        else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
+                    } else {
+                        const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
+                        for (int kk = 0; kk < nsteps; ++kk)
+                            ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                    }
+                }
+#ifdef BI_TC_PROFILE
+                const long long tq2 = clock64();
+#endif
+                ptx::umma_commit(bar_done(it.d));
+#ifdef BI_TC_PROFILE
+                const long long tq3 = clock64();
+                prof_fence += tq1 - tq0; prof_mma += tq2 - tq1; prof_commit += tq3 - tq2;
+#endif
             }
+#ifdef BI_TC_PROFILE
+            if (p.status) {
+                unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
+                atomicAdd(c + 8, (unsigned long long)prof_fence); atomicAdd(c + 9, (unsigned long long)prof_mma);
+                atomicAdd(c + 10, (unsigned long long)prof_commit);
+            }
+#endif
         }
     } else if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4) {
         // ------------------------------------------------------------ epilogue
-        const int quad = warp & 3;  // TMEM lanes this warp may read: 32*quad .. 32*quad+31
+        const int quad = warp & 3;  // TMEM lanes this warp may touch: 32*quad .. 32*quad+31
         const int row = quad * 32 + lane;
-        long long job = 0; bool ok = true;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        int job = -1; bool ok = true;
         T* out = static_cast<T*>(p.out);
-        for (long long u = ub; u < ue && ok; ++u) {
-            const Unit un = decode_unit(p, u);
-            const int n = un.n0 + row;
-            const int ncols = min(BLOCK_M, p.M - un.m0);
-            float total[BLOCK_M];
+        for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
+            if (it.first_in_group()) ++job;
+            if (!it.last_in_group()) continue;
+            const int buf = job & 1;
+            if (!wait_bounded(bar_done(it.d), it.dph, ctl, ROLE_EPI, 16 + it.d)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const int g = it.g;
+            const int n = it.n0() + row;
+            const int m0 = it.m0();
+            const int ncols = min(BLOCK_M, p.M - m0);
+            const uint32_t acc = lane_base + (uint32_t)buf * TMEM_ACC1;
+            const bool first = g == 0, last = g == p.G - 1;
+#pragma unroll 1
+            for (int c = 0; c * 32 < ncols; ++c) {  // warp-uniform trip count
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(acc + c * 32, v);
+                if (p.split) {
+                    ptx::tmem_ld_wait();
+                    if (n < p.N) {
 #pragma unroll
-            for (int i = 0; i < BLOCK_M; ++i) total[i] = 0.0f;
-            for (int g = un.g0; g < un.g1 && ok; ++g, ++job) {
-                const int buf = (int)(job & 1);
-                if (!wait_bounded(bar_tfull(buf), (uint32_t)((job >> 1) & 1), ctl, ROLE_EPI, 16 + buf)) { ok = false; break; }
-                ptx::tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)buf * BLOCK_M;
-#pragma unroll
-                for (int c = 0; c < BLOCK_M / 32; ++c) {
-                    if (c * 32 < ncols) {  // warp-uniform
-                        uint32_t v[32];
-                        ptx::tmem_ld_32x32(taddr + c * 32, v);
-                        ptx::tmem_ld_wait();
-                        if (p.split) {
-                            if (n < p.N) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    const int m = un.m0 + c * 32 + j;
-                                    if (m < p.M) p.part[((long long)g * p.M + m) * p.N + n] = __uint_as_float(v[j]);
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) total[c * 32 + j] = add_rn(total[c * 32 + j], __uint_as_float(v[j]));
+                        for (int j = 0; j < 32; ++j) {
+                            const int m = m0 + c * 32 + j;
+                            if (m < p.M) p.part[((long long)g * p.M + m) * p.N + n] = __uint_as_float(v[j]);
                         }
                     }
-                }
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
-            }
-            if (!p.split && ok && n < p.N) {
+                } else {
+                    // fused: the running total lives in TMEM; total = total + p_g, from an exact 0
+                    uint32_t t[32];
+                    if (!first) ptx::tmem_ld_32x32(lane_base + TMEM_TOTAL + c * 32, t);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < BLOCK_M; ++i) {
-                    const int m = un.m0 + i;
-                    if (i < ncols) out[(long long)m * p.N + n] = Cvt<T>::down(total[i]);
+                    for (int j = 0; j < 32; ++j)
+                        t[j] = __float_as_uint(add_rn(first ? 0.0f : __uint_as_float(t[j]), __uint_as_float(v[j])));
+                    if (last) {
+                        if (n < p.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int m = m0 + c * 32 + j;
+                                if (m < p.M) out[(long long)m * p.N + n] = Cvt<T>::down(__uint_as_float(t[j]));
+                            }
+                        }
+                    } else {
+                        ptx::tmem_st_32x32(lane_base + TMEM_TOTAL + c * 32, t);
+                    }
                 }
             }
+            if (!p.split && !last) ptx::tmem_st_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
         }
     } else if (QBITS && warp >= WARP_DEQ0) {
         // ------------------------------------------------------------ dequantizers
+        // 256 threads: thread t turns half a weight row (32 codes) of every K step into four
+        // 16-byte chunks of the swizzled tile. Two threads per row, so a warp reads 512 contiguous
+        // bytes of packed codes and its stores spread over all banks.
         constexpr int QB = QBITS ? QBITS : 4;
-        constexpr int ROW_BYTES = BLOCK_K * QB / 8;     // packed bytes per weight row per stage
-        constexpr int WORDS_PER_CHUNK = QB / 4;         // 32-bit words behind one 16-byte output chunk
-        const int row = (warp - WARP_DEQ0) * 32 + lane;
+        constexpr int ROW_BYTES = BLOCK_K * QB / 8;     // packed bytes per weight row per K step
+        constexpr int HALF_WORDS = ROW_BYTES / 8;       // 32-bit words behind 32 codes
+        constexpr int WORDS_PER_CHUNK = QB / 4;
+        const int t = threadIdx.x - WARP_DEQ0 * 32;
+        const int row = t >> 1, half = t & 1;
         const T* scales = static_cast<const T*>(p.scales);
         const T* biases = static_cast<const T*>(p.biases);
         const int groups_per_row = p.K / p.gs;
-        int s = 0; uint32_t ph = 0; bool ok = true;
-        for (long long u = ub; u < ue && ok; ++u) {
-            const Unit un = decode_unit(p, u);
-            const int n = un.n0 + row;
-            const bool live = n < p.N;
-            for (int g = un.g0; g < un.g1 && ok; ++g) {
-                const int nst = stages_in_group(p, g);
-                for (int ks = 0; ks < nst; ++ks) {
-                    const int k0 = g * GROUP_K + ks * BLOCK_K;
-                    // scale / bias of the (at most two) quantization groups this stage touches
-                    float sc[2] = {0.0f, 0.0f}, bs[2] = {0.0f, 0.0f};
-                    if (live) {
-                        const long long gi = (long long)n * groups_per_row + k0 / p.gs;
-                        sc[0] = Cvt<T>::up(scales[gi]); bs[0] = Cvt<T>::up(biases[gi]);
-                        if (p.gs == 32) { sc[1] = Cvt<T>::up(scales[gi + 1]); bs[1] = Cvt<T>::up(biases[gi + 1]); }
-                        else            { sc[1] = sc[0]; bs[1] = bs[0]; }
-                    }
-                    if (!wait_bounded(bar_raw(s), ph, ctl, ROLE_DEQ, s)) { ok = false; break; }
-                    const uint4* raw = reinterpret_cast<const uint4*>(smem_gen + (raw_tile(s) - smem_base) + row * ROW_BYTES);
-                    uint8_t* wt = smem_gen + (w_tile(s) - smem_base) + row * 128;
-                    uint32_t rw[ROW_BYTES / 4];
+        const int per_group = GROUP_K / p.gs;              // 8, 4 or 2 quantization groups per K group
+        const int gs_shift = p.gs == 32 ? 5 : (p.gs == 64 ? 6 : 7);
+        constexpr int NQ = GROUP_K / 32;
+        float scv[NQ], bsv[NQ];
+        bool ok = true;
+        for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
+            if (it.first_in_group()) {
+                // scale / bias of every quantization group this K group touches, fetched once per K group
+                const int n = it.n0() + row;
+                const bool live = n < p.N;
+                const int q0 = (it.g * GROUP_K) / p.gs;
+                const long long gi0 = (long long)n * groups_per_row + q0;
+                const int have = min(per_group, groups_per_row - q0);
 #pragma unroll
-                    for (int i = 0; i < ROW_BYTES / 16; ++i) {
-                        const uint4 t = raw[i];
-                        rw[4 * i] = t.x; rw[4 * i + 1] = t.y; rw[4 * i + 2] = t.z; rw[4 * i + 3] = t.w;
-                    }
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint32_t words[2];
-                        words[0] = rw[c * WORDS_PER_CHUNK];
-                        words[1] = rw[c * WORDS_PER_CHUNK + (WORDS_PER_CHUNK - 1)];
-                        const uint4 o = dequant8<T, QB>(words, sc[c >> 2], bs[c >> 2]);
-                        *reinterpret_cast<uint4*>(wt + ((c ^ (row & 7)) << 4)) = o;
-                    }
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar_full(s));
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                for (int i = 0; i < NQ; ++i) {
+                    const bool on = live && i < have;
+                    scv[i] = on ? Cvt<T>::up(scales[gi0 + i]) : 0.0f;
+                    bsv[i] = on ? Cvt<T>::up(biases[gi0 + i]) : 0.0f;
                 }
             }
+            const int l = it.l, w = it.w;
+            if (!wait_bounded(bar_lfull(l), it.lph, ctl, ROLE_DEQ, l)) { ok = false; break; }
+            if (it.ci >= WS && !wait_done(it.ci - WS, ROLE_DEQ)) { ok = false; break; }
+            const int kc = it.ksteps();
+            for (int j = 0; j < kc; ++j) {
+                const int qi = ((it.c * KS + j) * BLOCK_K + half * 32) >> gs_shift;  // index inside this K group
+                float sc = scv[0], bs = bsv[0];
+#pragma unroll
+                for (int i = 1; i < NQ; ++i)
+                    if (qi == i) { sc = scv[i]; bs = bsv[i]; }
+                const uint64_t s2 = ptx::pack2(sc, sc), b2 = ptx::pack2(bs, bs);
+                const uint4* raw = reinterpret_cast<const uint4*>(smem_gen + (raw_tile(l, j) - smem_base) + row * ROW_BYTES + half * (ROW_BYTES / 2));
+                uint32_t rw[HALF_WORDS];
+#pragma unroll
+                for (int i = 0; i < HALF_WORDS / 4; ++i) {
+                    const uint4 q = raw[i];
+                    rw[4 * i] = q.x; rw[4 * i + 1] = q.y; rw[4 * i + 2] = q.z; rw[4 * i + 3] = q.w;
+                }
+                uint8_t* wt = smem_gen + (w_tile(w, j) - smem_base) + row * 128;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int c = half * 4 + jj;
+                    const uint4 o = dequant8<T, QB>(&rw[jj * WORDS_PER_CHUNK], s2, b2);
+                    *reinterpret_cast<uint4*>(wt + ((c ^ (row & 7)) << 4)) = o;
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_wfull(w));
         }
     }
 
+#ifdef BI_TC_PROFILE
+    // development build: status is an array of 16 int64 counters (per role: waited, busy)
+    if (p.status && lane == 0) {
+        const int role = warp == WARP_TMA ? 0 : warp == WARP_MMA ? 1 : warp == WARP_EPI0 ? 2 : warp == WARP_DEQ0 ? 3 : -1;
+        if (role >= 0) {
+            unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
+            atomicAdd(c + 2 * role, (unsigned long long)waited);
+            atomicAdd(c + 2 * role + 1, (unsigned long long)(clock64() - t_start));
+        }
+    }
+#endif
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == WARP_MMA) {
@@ -423,20 +598,35 @@ int sm_count() {
 }
 
 template <typename T, int QBITS>
-int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cudaStream_t st) {
+int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, Params p, cudaStream_t st) {
     using C = Cfg<QBITS>;
     auto kern = tc_matmul_kernel<T, QBITS>;
+    // Chunk size and ring depths from the shared-memory budget (a launch-shape choice; no arithmetic
+    // depends on it): the largest chunk that still leaves at least two slots in every ring.
+    const int avail = SMEM_LIMIT - 1024 - BAR_BYTES;
+    p.w_slots = QBITS ? 2 : 0;
+    p.ks = 0;
+    for (int ks = 4; ks >= 1; ks >>= 1) {
+        const int wring = p.w_slots * ks * W_TILE_BYTES;
+        const int slot = ks * (p.x_bytes + (QBITS ? C::RAW_BYTES : W_TILE_BYTES));
+        const int ls = (avail - wring) / slot;
+        if (ls >= 2) { p.ks = ks; p.load_slots = ls < MAX_SLOTS ? ls : MAX_SLOTS; break; }
+    }
+    if (!p.ks) return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
+    p.w_ring_slots = QBITS ? p.w_slots : p.load_slots;
+    const int smem_bytes = 1024 + BAR_BYTES + p.load_slots * p.ks * (p.x_bytes + C::RAW_BYTES) +
+                           (QBITS ? p.w_slots : p.load_slots) * p.ks * W_TILE_BYTES;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
         if (e != cudaSuccess) return fail(BI_ERR_CUDA, "matmul smem attr: %s", cudaGetErrorString(e));
         attr_done[dev] = true;
     }
     const long long grid = p.units < sm_count() ? p.units : sm_count();
-    kern<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, st>>>(mw, mx, p);
+    kern<<<(unsigned)grid, C::THREADS, smem_bytes, st>>>(mw, mx, p);
     return check_launch("matmul (tensor-core path)");
 }
 
@@ -471,9 +661,11 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     p.split = split ? 1 : 0;
     p.gs = quant ? q->gs : 0;
     p.units = (long long)p.n_tiles * p.m_tiles * (split ? p.G : 1);
+    if (p.units >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "matmul: %lld work units exceed the kernel's 32-bit unit index", p.units);
     // Only the batch rows that exist are loaded; the box height is a launch-shape choice.
     const int64_t mr = M < BLOCK_M ? ((M + 7) / 8) * 8 : BLOCK_M;
     p.x_rows = (int)mr;
+    p.x_bytes = ((int)mr * BLOCK_K * 2 + 1023) / 1024 * 1024;
 
     const CUtensorMapDataType dt = dtype == BI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mw, mx;
