@@ -29,6 +29,7 @@
 // functions (merge_coeffs / merge_acc for the split fold), which is why a token's bits do not depend on which of the two
 // produced it.
 #include "bi_common.cuh"
+#include "bi_ptx.cuh"
 
 namespace bi {
 namespace {
@@ -196,6 +197,226 @@ __global__ void __launch_bounds__(128) decode_kernel(const T* __restrict__ q, co
 #pragma unroll
                     for (int d = 0; d < DL; ++d)
                         pacc[po * D + (r + OCT * j) * DL + d] = acc[iq][j * DL + d];
+            }
+        }
+    }
+}
+
+// ---- decode, streamed: same units and arithmetic as decode_kernel; K/V rows reach the lanes through a
+// per-warp ring of shared-memory stages filled by 16-byte cp.async copies, so several keys per stream
+// are in flight while one is processed. The fp32 work runs as packed f32x2 instructions (two
+// independent round-to-nearest operations each: same bits as the scalar forms), pairing virtual
+// lanes (r, r+8) and (r+16, r+24); and the scalar softmax step of a head is evaluated on one lane of
+// the octet and handed to the others by shuffle instead of being repeated on all eight.
+constexpr int DEC2_KC = 2;       // keys per stream per stage
+constexpr int DEC2_STAGES = 4;
+constexpr int DEC2_WARPS = 4;
+
+template <typename T, int DL> struct Dec2Cfg {
+    static constexpr int ROWB = 32 * DL * (int)sizeof(T);                  // bytes of one K or V row
+    static constexpr int PITCH = ROWB + 64;                                // rows of the 4 streams land on different banks
+    static constexpr int ROWS = 2 * DEC2_KC * OCT_PER_WARP;                // rows per stage: (k|v, key, stream)
+    static constexpr int STAGE_BYTES = ROWS * PITCH;
+    static constexpr int WARP_BYTES = DEC2_STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = DEC2_WARPS * WARP_BYTES;
+};
+
+// two T values (consecutive dims) packed in one 32-bit word -> fp32, for 16-bit T
+template <typename T> __device__ __forceinline__ float word_lo(uint32_t w);
+template <typename T> __device__ __forceinline__ float word_hi(uint32_t w);
+template <> __device__ __forceinline__ float word_lo<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w << 16); }
+template <> __device__ __forceinline__ float word_hi<__nv_bfloat16>(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+template <> __device__ __forceinline__ float word_lo<__half>(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFFu))); }
+template <> __device__ __forceinline__ float word_hi<__half>(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+
+// Slice of a row owned by real lane r, as packed pairs: dst[jp][d] = (x[(r + 16 jp) * DL + d], x[(r + 8 + 16 jp) * DL + d])
+template <typename T, int DL>
+__device__ __forceinline__ void load_slice_pairs(const uint8_t* row, int r, uint64_t (&dst)[2][DL]) {
+    float f[NCHUNK][DL];
+#pragma unroll
+    for (int j = 0; j < NCHUNK; ++j) {
+        const uint8_t* c = row + (r + OCT * j) * DL * sizeof(T);
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int d = 0; d < DL; ++d) f[j][d] = reinterpret_cast<const float*>(c)[d];
+        } else if constexpr (DL == 1) {
+            f[j][0] = Cvt<T>::up(*reinterpret_cast<const T*>(c));
+        } else {
+#pragma unroll
+            for (int d2 = 0; d2 < DL / 2; ++d2) {
+                const uint32_t w = reinterpret_cast<const uint32_t*>(c)[d2];
+                f[j][2 * d2] = word_lo<T>(w);
+                f[j][2 * d2 + 1] = word_hi<T>(w);
+            }
+        }
+    }
+#pragma unroll
+    for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+        for (int d = 0; d < DL; ++d) dst[jp][d] = ptx::pack2(f[2 * jp][d], f[2 * jp + 1][d]);
+}
+
+template <typename T, int DL, int GU>
+__global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
+    float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
+    KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    using C = Dec2Cfg<T, DL>;
+    constexpr int D = 32 * DL;
+    constexpr int SEGS = C::ROWB / 16;                 // 16-byte segments per row
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    __shared__ const T* s_kb[DEC2_WARPS][OCT_PER_WARP];
+    __shared__ const T* s_vb[DEC2_WARPS][OCT_PER_WARP];
+    __shared__ int s_nk[DEC2_WARPS][OCT_PER_WARP];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane & (OCT - 1), o = lane >> 3;
+    uint8_t* ring = dec_smem + wid * C::WARP_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+
+    const long long oct = ((long long)blockIdx.x * DEC2_WARPS + wid) * OCT_PER_WARP + o;
+    const long long units = (long long)B * Hkv * nchunk * nsplit;
+    const bool unit_ok = oct < units;
+    long long u = unit_ok ? oct : 0;
+    const int sp = (int)(u % nsplit); u /= nsplit;
+    const int chunk = (int)(u % nchunk); u /= nchunk;
+    const int hk = (int)(u % Hkv); u /= Hkv;
+    const int b = (int)u;
+    const int G = Hq / Hkv;
+    const int h0 = hk * G + chunk * GU;
+    const int gcount = min(GU, G - chunk * GU);
+    const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+    const int j0 = sp * split;
+    const int nk = (unit_ok && j0 < Lb) ? (min(Lb, j0 + split) - j0) : 0;
+    if (r == 0) {
+        s_kb[wid][o] = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+        s_vb[wid][o] = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+        s_nk[wid][o] = nk;
+    }
+    __syncwarp();
+    int nk_max = nk;
+    nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 8));
+    nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 16));
+    const int nstage = (nk_max + DEC2_KC - 1) / DEC2_KC;
+
+    // copy stage `st` (keys st*KC .. st*KC+KC-1 of every stream) into ring slot st % STAGES
+    auto issue = [&](int st) {
+        if (st < nstage) {
+            const uint32_t dst0 = ring_s + (uint32_t)(st % DEC2_STAGES) * C::STAGE_BYTES;
+#pragma unroll
+            for (int t = 0; t < C::ROWS * SEGS / 32; ++t) {
+                const int idx = lane + 32 * t;
+                const int seg = idx % SEGS, row = idx / SEGS;          // row = (kv * KC + key) * 4 + stream
+                const int so = row & 3, key = (row >> 2) % DEC2_KC, kv = row / (4 * DEC2_KC);
+                const int jj = min(st * DEC2_KC + key, max(s_nk[wid][so] - 1, 0));   // past the stream's end: re-read a valid row
+                const T* base = kv ? s_vb[wid][so] : s_kb[wid][so];
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(base + (int64_t)jj * lay.sl) + seg * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * C::PITCH + seg * 16), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // queries of this unit, pre-scaled, as packed pairs
+    uint64_t qp[GU][2][DL];
+#pragma unroll
+    for (int iq = 0; iq < GU; ++iq) {
+        const T* qr = q + ((int64_t)b * Hq + h0 + min(iq, gcount - 1)) * D;
+        float qf[NCHUNK * DL];
+        load_slice<T, DL>(qr, r, qf);
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+            for (int d = 0; d < DL; ++d)
+                qp[iq][jp][d] = ptx::pack2(mul_rn(qf[(2 * jp) * DL + d], scale), mul_rn(qf[(2 * jp + 1) * DL + d], scale));
+    }
+    uint64_t accp[GU][2][DL];
+#pragma unroll
+    for (int iq = 0; iq < GU; ++iq)
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+            for (int d = 0; d < DL; ++d) accp[iq][jp][d] = ptx::pack2(0.0f, 0.0f);
+    // lane r keeps the softmax scalars (m, l) of head r % GU only
+    const int my_head = r % GU;
+    float m_own = -INFINITY, l_own = 0.0f;
+
+    for (int st = 0; st < DEC2_STAGES - 1; ++st) issue(st);
+    for (int st = 0; st < nstage; ++st) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(DEC2_STAGES - 2) : "memory");
+        __syncwarp();
+        const uint8_t* stage = ring + (st % DEC2_STAGES) * C::STAGE_BYTES;
+#pragma unroll
+        for (int key = 0; key < DEC2_KC; ++key) {
+            const int jj = st * DEC2_KC + key;
+            if (jj >= nk_max) break;                       // warp-uniform
+            const bool on = jj < nk;
+            uint64_t kp[2][DL], vp[2][DL];
+            load_slice_pairs<T, DL>(stage + (key * 4 + o) * C::PITCH, r, kp);
+            load_slice_pairs<T, DL>(stage + ((DEC2_KC + key) * 4 + o) * C::PITCH, r, vp);
+            // scores of the GU heads: packed fma chains, tree levels 16 and 8 local, 4-2-1 by shuffle
+            float s[GU];
+#pragma unroll
+            for (int iq = 0; iq < GU; ++iq) {
+                uint64_t p01 = ptx::pack2(0.0f, 0.0f), p23 = ptx::pack2(0.0f, 0.0f);
+#pragma unroll
+                for (int d = 0; d < DL; ++d) {
+                    p01 = ptx::fma2_rn(qp[iq][0][d], kp[0][d], p01);   // virtual lanes r, r+8
+                    p23 = ptx::fma2_rn(qp[iq][1][d], kp[1][d], p23);   // virtual lanes r+16, r+24
+                }
+                float a0, a1;
+                ptx::unpack2(ptx::add2_rn(p01, p23), a0, a1);          // (part_r + part_{r+16}, part_{r+8} + part_{r+24})
+                float t = add_rn(a0, a1);
+                t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 4));
+                t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
+                t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
+                s[iq] = t;
+            }
+            // softmax step of head `my_head` on this lane
+            float s_own = s[0];
+#pragma unroll
+            for (int iq = 1; iq < GU; ++iq) if (my_head == iq) s_own = s[iq];
+            const float m_new = fmaxf(m_own, s_own);
+            const float e = expf_canon(-fabsf(sub_rn(s_own, m_own)));
+            const bool rises = s_own >= m_own;
+            const float corr_own = rises ? e : 1.0f;
+            const float p_own = rises ? 1.0f : e;
+            const bool upd = on && my_head < gcount;
+            if (upd) { l_own = fma_rn(l_own, corr_own, p_own); m_own = m_new; }
+#pragma unroll
+            for (int iq = 0; iq < GU; ++iq) {
+                const int src = (lane & 24) | iq;
+                const float corr = __shfl_sync(0xffffffffu, corr_own, src);
+                const float pw = __shfl_sync(0xffffffffu, p_own, src);
+                if (on && iq < gcount) {
+                    const uint64_t c2 = ptx::pack2(corr, corr), p2 = ptx::pack2(pw, pw);
+#pragma unroll
+                    for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+                        for (int d = 0; d < DL; ++d)
+                            accp[iq][jp][d] = ptx::fma2_rn(accp[iq][jp][d], c2, ptx::mul2_rn(p2, vp[jp][d]));
+                }
+            }
+        }
+        __syncwarp();
+        issue(st + DEC2_STAGES - 1);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+
+    if (nk > 0) {
+#pragma unroll
+        for (int iq = 0; iq < GU; ++iq) {
+            if (iq < gcount) {
+                const int64_t po = ((int64_t)b * Hq + h0 + iq) * nsplit + sp;
+                if (r == iq) { pm[po] = m_own; pl[po] = l_own; }
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+                    for (int d = 0; d < DL; ++d) {
+                        float lo, hi;
+                        ptx::unpack2(accp[iq][jp][d], lo, hi);
+                        pacc[po * D + (r + OCT * (2 * jp)) * DL + d] = lo;
+                        pacc[po * D + (r + OCT * (2 * jp + 1)) * DL + d] = hi;
+                    }
             }
         }
     }
@@ -398,6 +619,34 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
     const T* kp = static_cast<const T*>(k);
     const T* vp = static_cast<const T*>(v);
     dim3 grid((unsigned)blocks), block(32 * warps);
+    // Streamed kernel when every K/V row starts on a 16-byte boundary (cp.async granularity);
+    // otherwise the register-prefetch kernel. Same arithmetic, the choice depends on layout only.
+    if constexpr (DL < 8) {
+        const int64_t per16 = 16 / (int64_t)sizeof(T);
+        const bool rows16 = aligned(k, 16) && aligned(v, 16) && lay.sb % per16 == 0 && lay.sh % per16 == 0 &&
+                            lay.sl % per16 == 0 && (32 * DL * sizeof(T)) % 16 == 0;
+        if (rows16) {
+            using C = Dec2Cfg<T, DL>;
+            const int64_t blocks2 = (units + DEC2_WARPS * OCT_PER_WARP - 1) / (DEC2_WARPS * OCT_PER_WARP);
+#define BI_DECODE2_LAUNCH(GUV)                                                                                   \
+    do {                                                                                                         \
+        auto kern = decode_stream_kernel<T, DL, GUV>;                                                            \
+        if (C::SMEM_BYTES > 40 * 1024) { /* static shared memory counts toward the 48 KB default too */          \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); \
+            if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e)); \
+        }                                                                                                        \
+        kern<<<(unsigned)blocks2, 32 * DEC2_WARPS, C::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, \
+                                                                          (int)Hq, (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk); \
+    } while (0)
+            if (GU == 4) BI_DECODE2_LAUNCH(4); else if (GU == 2) BI_DECODE2_LAUNCH(2); else BI_DECODE2_LAUNCH(1);
+#undef BI_DECODE2_LAUNCH
+            int rc2 = check_launch("bi_attn_decode (streamed)");
+            if (rc2) return rc2;
+            const int64_t n2s = BH * D;
+            decode_combine_kernel<T><<<(unsigned)((n2s + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
+            return check_launch("bi_attn_decode combine");
+        }
+    }
 #define BI_DECODE_LAUNCH(GUV)                                                                              \
     decode_kernel<T, DL, GUV><<<grid, block, 0, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
                                                       (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk)
