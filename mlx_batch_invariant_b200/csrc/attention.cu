@@ -208,8 +208,8 @@ __global__ void __launch_bounds__(128) decode_kernel(const T* __restrict__ q, co
 // independent round-to-nearest operations each: same bits as the scalar forms), pairing virtual
 // lanes (r, r+8) and (r+16, r+24); and the scalar softmax step of a head is evaluated on one lane of
 // the octet and handed to the others by shuffle instead of being repeated on all eight.
-constexpr int DEC2_KC = 2;       // keys per stream per stage
-constexpr int DEC2_STAGES = 4;
+constexpr int DEC2_KC = 4;       // keys per stream per stage
+constexpr int DEC2_STAGES = 2;
 constexpr int DEC2_WARPS = 4;
 
 template <typename T, int DL> struct Dec2Cfg {
@@ -265,9 +265,6 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
     constexpr int D = 32 * DL;
     constexpr int SEGS = C::ROWB / 16;                 // 16-byte segments per row
     extern __shared__ __align__(16) uint8_t dec_smem[];
-    __shared__ const T* s_kb[DEC2_WARPS][OCT_PER_WARP];
-    __shared__ const T* s_vb[DEC2_WARPS][OCT_PER_WARP];
-    __shared__ int s_nk[DEC2_WARPS][OCT_PER_WARP];
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane & (OCT - 1), o = lane >> 3;
     uint8_t* ring = dec_smem + wid * C::WARP_BYTES;
@@ -287,30 +284,31 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
     const int Lb = kv_lens ? min(kv_lens[b], L) : L;
     const int j0 = sp * split;
     const int nk = (unit_ok && j0 < Lb) ? (min(Lb, j0 + split) - j0) : 0;
-    if (r == 0) {
-        s_kb[wid][o] = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
-        s_vb[wid][o] = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
-        s_nk[wid][o] = nk;
-    }
-    __syncwarp();
     int nk_max = nk;
     nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 8));
     nk_max = max(nk_max, __shfl_xor_sync(0xffffffffu, nk_max, 16));
     const int nstage = (nk_max + DEC2_KC - 1) / DEC2_KC;
 
-    // copy stage `st` (keys st*KC .. st*KC+KC-1 of every stream) into ring slot st % STAGES
+    // copy stage `st` (keys st*KC .. st*KC+KC-1 of every stream) into ring slot st % STAGES. Each octet
+    // copies its own stream's rows: eight lanes x 16 bytes = 128 contiguous bytes per instruction.
+    const T* const kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+    const T* const vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+    const int last_key = max(nk - 1, 0);               // past the stream's end: re-read a valid row
     auto issue = [&](int st) {
         if (st < nstage) {
-            const uint32_t dst0 = ring_s + (uint32_t)(st % DEC2_STAGES) * C::STAGE_BYTES;
+            const uint32_t dst0 = ring_s + (uint32_t)(st % DEC2_STAGES) * C::STAGE_BYTES + (uint32_t)o * C::PITCH + r * 16;
 #pragma unroll
-            for (int t = 0; t < C::ROWS * SEGS / 32; ++t) {
-                const int idx = lane + 32 * t;
-                const int seg = idx % SEGS, row = idx / SEGS;          // row = (kv * KC + key) * 4 + stream
-                const int so = row & 3, key = (row >> 2) % DEC2_KC, kv = row / (4 * DEC2_KC);
-                const int jj = min(st * DEC2_KC + key, max(s_nk[wid][so] - 1, 0));   // past the stream's end: re-read a valid row
-                const T* base = kv ? s_vb[wid][so] : s_kb[wid][so];
-                const uint8_t* src = reinterpret_cast<const uint8_t*>(base + (int64_t)jj * lay.sl) + seg * 16;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * C::PITCH + seg * 16), "l"(src) : "memory");
+            for (int key = 0; key < DEC2_KC; ++key) {
+                const int64_t off = (int64_t)min(st * DEC2_KC + key, last_key) * lay.sl;
+                const uint8_t* ks = reinterpret_cast<const uint8_t*>(kb + off) + r * 16;
+                const uint8_t* vs = reinterpret_cast<const uint8_t*>(vb + off) + r * 16;
+#pragma unroll
+                for (int sg = 0; sg < SEGS; sg += OCT) {
+                    if (SEGS >= OCT || r < SEGS) {
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + (key * 4) * C::PITCH + sg * 16), "l"(ks + sg * 16) : "memory");
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + ((DEC2_KC + key) * 4) * C::PITCH + sg * 16), "l"(vs + sg * 16) : "memory");
+                    }
+                }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -343,7 +341,8 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
     for (int st = 0; st < DEC2_STAGES - 1; ++st) issue(st);
     for (int st = 0; st < nstage; ++st) {
         asm volatile("cp.async.wait_group %0;" ::"n"(DEC2_STAGES - 2) : "memory");
-        __syncwarp();
+        __syncwarp();                                      // stage st visible; slot of stage st-1 free
+        issue(st + DEC2_STAGES - 1);
         const uint8_t* stage = ring + (st % DEC2_STAGES) * C::STAGE_BYTES;
 #pragma unroll
         for (int key = 0; key < DEC2_KC; ++key) {
@@ -397,8 +396,6 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
                 }
             }
         }
-        __syncwarp();
-        issue(st + DEC2_STAGES - 1);
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 
@@ -609,7 +606,11 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
     float* pacc = pl + BH * nsplit;
     // Query heads of a kv head share each K/V row load, up to four per unit.
     // How they are grouped is a launch choice; a head's arithmetic is the same alone or grouped.
-    const int GU = (G >= 4 && DL < 8) ? 4 : (G >= 2 ? 2 : 1);
+    // With few units the GPU is short of independent key streams, so the heads of a kv head stop
+    // sharing a stream (the rows are then re-read through L2) until there are enough.
+    int GU = (G >= 4 && DL < 8) ? 4 : (G >= 2 ? 2 : 1);
+    const int64_t enough = 148 * 16;
+    while (GU > 1 && B * Hkv * ((G + GU - 1) / GU) * nsplit < enough) GU >>= 1;
     const int nchunk = (G + GU - 1) / GU;
     const int64_t units = B * Hkv * nchunk * nsplit;
     const int warps = 4;
