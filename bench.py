@@ -2,10 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-One "step" is one pass of the workload's op over one batch of seeded synthetic input.
+One "step" is one pass of the workload over one batch of seeded synthetic input.
 Prints ONE JSON line (rank 0). Workloads:
 
-    matmul_bf16_m256   dense y = x @ W^T, x[256,4096], W[4096,4096], bf16     -> TFLOP/s   (default)
+    llama3_8b_decode   Llama-3-8B-architecture decoder, random init, bf16, batch 64, 512-token prompts:
+                       one step = one greedy decode step of all 64 sequences                -> tok/s (default)
+                       sharded column/head-parallel over --gpus N with all-gather (strong scaling)
+    llama3_8b_decode_q4  the same with 4-bit group-64 weights
+    matmul_bf16_m256   dense y = x @ W^T, x[256,4096], W[4096,4096], bf16     -> TFLOP/s
     qmm4_decode        4-bit group-64 quantized matmul, M=1, K=4096 -> N=14336  -> GB/s
     attn_decode        decode attention, bf16, 32/8 heads, D=128, B=64, L=4096  -> GB/s
     rms_norm           RMSNorm [256,4096] bf16                                  -> GB/s
@@ -14,7 +18,8 @@ Timing: CUDA events on the launching stream, W >= 3 warm-up steps, inputs rotate
 distinct buffers than fit in L2 so every step streams from HBM, max over ranks. `value` has
 inputs resident in HBM; `e2e` goes through the public API from pinned host buffers and back.
 With --gpus N > 1 the op-level workloads run as N independent replicas (no collective: the
-op itself does not shard), value = sum over ranks / max time.
+op itself does not shard), value = sum over ranks / max time; the decoder workloads shard the
+model (every linear by weight rows, attention by KV head) and join slices by NCCL all-gather.
 --impl reference times the CPU restatement of the reference algorithm (the oracle; the
 reference itself is Metal-only and cannot run here) on the host cores.
 """
@@ -386,7 +391,161 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if dist:
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
+# ---------------------------------------------------------------------------------------------
+# whole-model workload
+MODEL_B, MODEL_P = 64, 512
+
+
+def _model_bytes_per_step(cfg, quant, B, kv_tokens):
+    """Algorithmic bytes of one decode step: every linear weight once, the KV cache once."""
+    D = cfg.head_dim
+    per_layer = (cfg.n_heads * D + 2 * cfg.n_kv_heads * D) * cfg.d_model + cfg.d_model * cfg.n_heads * D + 3 * cfg.ffn * cfg.d_model
+    params = cfg.n_layers * per_layer + cfg.vocab * cfg.d_model
+    wbytes = params * (2.0 if quant is None else (quant[0] / 8 + 4 / quant[1]))
+    kv = cfg.n_layers * 2 * cfg.n_kv_heads * D * 2 * kv_tokens * B
+    return wbytes + kv
+
+
+def _cpu_tok_per_s(R, torch, cfg):
+    """Oracle port on a bounded sample: the four linears and RMSNorms of one layer plus the lm_head for
+    one token (CUDA-core order of the K-group algorithm), extrapolated to the 32 layers."""
+    g = torch.Generator().manual_seed(0)
+    dt = torch.bfloat16
+    D = cfg.head_dim
+    x = torch.randn(1, cfg.d_model, generator=g).to(dt)
+    shapes = [((cfg.n_heads + 2 * cfg.n_kv_heads) * D, cfg.d_model), (cfg.d_model, cfg.n_heads * D), (2 * cfg.ffn, cfg.d_model), (cfg.d_model, cfg.ffn)]
+    ws = [(torch.randn(n, k, generator=g) * 0.02).to(dt).T.contiguous() for n, k in shapes]
+    head = (torch.randn(cfg.vocab // 8, cfg.d_model, generator=g) * 0.02).to(dt).T.contiguous()
+    nw = torch.ones(cfg.d_model, dtype=dt)
+    t0 = time.perf_counter()
+    for w in ws:
+        a = torch.randn(1, w.shape[0], generator=g).to(dt)
+        R.rms_norm(a, None, 1e-5)
+        R.matmul_f32order(a, w)
+    t_layer = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    R.matmul_f32order(x, head)
+    t_head = (time.perf_counter() - t0) * 8
+    del nw
+    return 1.0 / (cfg.n_layers * t_layer + t_head), f"1 of {cfg.n_layers} layers' linears and 1/8 of the lm_head for one token, extrapolated ({t_layer + t_head / 8:.1f} s of CPU work)"
+
+
+def run_model(args, quant):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the library has no CPU path)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    barrier = (lambda: dist.barrier()) if dist else (lambda: None)
+
+    import mlx_batch_invariant_b200 as bi
+    from mlx_batch_invariant_b200 import _lib
+    from mlx_batch_invariant_b200.runner import LLAMA3_8B, GraphedDecoder, ShardedDecoder
+    _lib.load()
+    cfg = LLAMA3_8B
+    B, P = MODEL_B, MODEL_P
+    warm = max(args.warmup, 3)
+    total_steps = warm + args.steps * 2 + 8
+    model = ShardedDecoder(cfg, rank=rank, world=world, device=dev, quant=quant, max_batch=B, max_len=P + total_steps + 1)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (B, P), generator=g).to(dev)
+    logits = model.forward(prompts, 0)
+    gd = GraphedDecoder(model, B)
+    gd.start(logits.argmax(-1), P)
+    graphed = True
+    try:
+        gd.capture()
+    except Exception as e:                                  # a step that cannot be captured still runs eagerly
+        graphed = False
+        gd.graph = None
+        gd.start(logits.argmax(-1), P)
+        if rank == 0:
+            print(f"bench.py: CUDA-graph capture failed ({type(e).__name__}: {e}); timing eager steps", file=sys.stderr)
+    for _ in range(warm):
+        gd.step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    sec = timed_region(torch, lambda i: gd.step(), args.steps, barrier)
+    # end to end: this step's token ids from pinned host memory, next token ids back to the host, every step
+    tok_host = torch.zeros(B, 1, dtype=torch.long).pin_memory()
+    nxt_host = torch.zeros(B, 1, dtype=torch.long).pin_memory()
+    nxt_host.copy_(gd.tokens)
+    torch.cuda.synchronize()
+    def e2e_step(i):
+        tok_host.copy_(nxt_host)
+        gd.tokens.copy_(tok_host, non_blocking=True)
+        gd.step()
+        nxt_host.copy_(gd.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    sec_e2e = timed_region(torch, e2e_step, args.steps, barrier)
+    clocks = sampler.stop() if rank == 0 else {}
+    bi.check_device_status(dev)
+    fallbacks = bi.stats()["fallbacks"]
+    if dist:
+        t = torch.tensor([sec, sec_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec, sec_e2e = float(t[0]), float(t[1])
+    per, per_e2e = sec / args.steps, sec_e2e / args.steps
+    if rank == 0:
+        pk = peaks()
+        kv_tokens = P + warm + args.steps // 2
+        bytes_step = _model_bytes_per_step(cfg, quant, B, kv_tokens) / world      # per GPU
+        achieved = bytes_step / per / 1e9
+        launches = (cfg.n_layers * (4 * 2 + 2 + 2) + 3)                           # matmul(+combine) x4, rmsnorm x2, attention x2 per layer; head
+        from oracle import reference as R
+        cores = os.cpu_count() or 1
+        cv, sample = _cpu_tok_per_s(R, torch, cfg)
+        name = "llama3_8b_decode" + ("" if quant is None else "_q4")
+        line = {
+            "metric": "model tok/s", "value": round(B / per, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": round(per * 1e3, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16" if quant is None else "bf16 activations, 4-bit group-64 weights",
+            "data": "synthetic",
+            "config": {"workload": name, "architecture": "Llama-3-8B (32 layers, d 4096, 32/8 heads, head_dim 128, ffn 14336, vocab 128256), random init",
+                       "global_batch": B, "prompt_len": P, "decode": "greedy, KV cache, CUDA graph replay" if graphed else "greedy, KV cache, eager",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world}: weight-row / KV-head shards, NCCL all-gather",
+                       "l2": "15 GB of weights streamed per step (>> L2)"},
+            "clocks": clocks,
+            "e2e": {"value": round(B / per_e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
+                    "ms_per_step": round(per_e2e * 1e3, 4)},
+            "gpu_launches": launches * args.steps,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": f"of {pk['which']}",
+                         "kernel": "whole decode step per GPU: weights + KV cache bytes / step time"},
+            "cpu_baseline": {"value": round(cv, 4), "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "fallbacks": fallbacks,
+        }
+        print(json.dumps(line), flush=True)
+    _shutdown(torch, dist, [gd])
+
+
+def _shutdown(torch, dist, holders):
+    """Leave a multi-rank run without hanging: drop CUDA graphs that captured NCCL kernels, meet at a
+    barrier, then exit the process directly (tearing the NCCL communicator down while graphs that used
+    it were alive has been seen to block in the watchdog)."""
+    for h in holders:
+        h.graph = None
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_reference(args):
@@ -402,6 +561,23 @@ def run_reference(args):
     class _NoDev:                                          # build the workload's host-side inputs only
         pass
     # CPU-only construction of the same seeded inputs
+    if args.workload.startswith("llama3_8b_decode"):
+        from mlx_batch_invariant_b200.runner import LLAMA3_8B
+        vals = []
+        sample = ""
+        for i in range(args.warmup + args.steps):
+            v, sample = _cpu_tok_per_s(R, torch, LLAMA3_8B)
+            if i >= args.warmup:
+                vals.append(v)
+        v = statistics.mean(vals)
+        line = {"impl": "reference", "metric": "model tok/s", "value": round(v, 4), "unit": "tok/s",
+                "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 / v, 1),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, "global_batch": MODEL_B, "prompt_len": MODEL_P},
+                "cpu_baseline": {"value": round(v, 4), "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+                "e2e": {"value": round(v, 4), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
     wl_cls = WORKLOADS[args.workload]
     vals = []
     sample = ""
@@ -434,13 +610,22 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="matmul_bf16_m256", choices=list(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--workload", default="llama3_8b_decode", choices=["llama3_8b_decode", "llama3_8b_decode_q4"] + list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
+    model = args.workload.startswith("llama3_8b_decode")
+    if args.steps is None:
+        args.steps = 64 if model else 200
+    if args.warmup is None:
+        args.warmup = 5 if model else 10
     if args.impl == "reference":
+        if args.steps > 3 and model:
+            args.steps, args.warmup = min(args.steps, 3), min(args.warmup, 1)     # each CPU step is seconds long
         run_reference(args)
+    elif model:
+        run_model(args, (4, 64) if args.workload.endswith("_q4") else None)
     else:
         run_ours(args)
 

@@ -159,7 +159,7 @@ class ShardedDecoder:
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
     def _rope(self, x, pos):                       # x[B, H, T, D], pos[T] (long, device)
-        cos, sin = self.cos[pos][None, None], self.sin[pos][None, None]
+        cos, sin = self.cos.index_select(0, pos)[None, None], self.sin.index_select(0, pos)[None, None]
         xf = x.float()
         half = x.shape[-1] // 2
         rot = torch.cat([-xf[..., half:], xf[..., :half]], -1)
@@ -201,6 +201,81 @@ class ShardedDecoder:
         last = x.reshape(B, T, -1)[:, -1]
         h = self.ops.rms_norm(last.contiguous(), self.nf, cfg.eps)
         return self._gather(self._lin(h, self.head))
+
+
+class GraphedDecoder:
+    """Greedy decoding with the whole decode step captured once in a CUDA graph.
+
+    Everything that changes from step to step lives on the device -- the position, the per-sequence
+    key counts, the token buffer -- so one captured step is replayed for every token: the K/V rows are
+    written with an index tensor, RoPE gathers its angles by the same index, attention runs over the
+    cache capacity with ``kv_lens``, and the argmax feeds the next step's token buffer. The kernels see
+    exactly the calls an eager step makes, so logits are bit-identical to ``ShardedDecoder.forward``.
+    """
+
+    def __init__(self, model: ShardedDecoder, batch: int):
+        self.m, self.B = model, batch
+        dev = model.dev
+        self.tokens = torch.zeros(batch, 1, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        self.lens = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.logits = None
+        self.graph = None
+
+    @torch.no_grad()
+    def _step(self):
+        m, cfg, B, D = self.m, self.m.cfg, self.B, self.m.cfg.head_dim
+        scale = 1.0 / math.sqrt(D)
+        x = m.embed[self.tokens.reshape(-1)]
+        for li, L in enumerate(m.layers):
+            h = m.ops.rms_norm(x, L["n1"], cfg.eps)
+            qkv = m._lin(h, L["qkv"]).reshape(B, 1, m.hq + 2 * m.hkv, D).transpose(1, 2)
+            q = m._rope(qkv[:, :m.hq], self.pos)
+            k = m._rope(qkv[:, m.hq:m.hq + m.hkv], self.pos)
+            v = qkv[:, m.hq + m.hkv:]
+            m.kc[li][:B].index_copy_(2, self.pos, k)
+            m.vc[li][:B].index_copy_(2, self.pos, v.contiguous())
+            a = m.ops.decode_attention(q.contiguous(), m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
+            a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
+            x = x + m._gather(m._lin(a, L["o"]))
+            h = m.ops.rms_norm(x, L["n2"], cfg.eps)
+            gu = m._lin(h, L["gu"])
+            f = cfg.ffn // m.world
+            act = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+            x = x + m._gather(m._lin(m._gather(act), L["down"]))
+        h = m.ops.rms_norm(x, m.nf, cfg.eps)
+        logits = m._gather(m._lin(h, m.head))
+        self.tokens.copy_(logits.argmax(-1, keepdim=True))
+        self.pos.add_(1)
+        self.lens.add_(1)
+        return logits
+
+    def start(self, first_tokens: torch.Tensor, position: int):
+        """Continue from `position` (the prompt length) with `first_tokens` [B] as the next input."""
+        self.tokens.copy_(first_tokens.reshape(self.B, 1))
+        self.pos.fill_(position)
+        self.lens.fill_(position + 1)
+
+    def capture(self):
+        """Run one eager step (first-call set-up happens outside capture), rewind, then capture."""
+        saved = (self.tokens.clone(), self.pos.clone(), self.lens.clone())
+        self._step()
+        torch.cuda.synchronize(self.m.dev)
+        for dst, src in zip((self.tokens, self.pos, self.lens), saved):
+            dst.copy_(src)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._step()
+        for dst, src in zip((self.tokens, self.pos, self.lens), saved):
+            dst.copy_(src)
+
+    def step(self):
+        """Advance every sequence by one token; returns the (static) logits tensor of this step."""
+        if self.graph is None:
+            self.logits = self._step()
+        else:
+            self.graph.replay()
+        return self.logits
 
 
 @torch.no_grad()

@@ -1,0 +1,79 @@
+"""Whole-model invariance on one GPU: the method of the reference's model sweep (harness/model_sweep.py:100-108
+there) on a small random-init Llama-architecture decoder. The prompt sits in row 0, the other rows are random
+prompts of the same length; every block's row-0 output and the logits must be bit-identical at batch 1, 4 and
+16, for the prefill and for cached decode steps, dense and 4-bit, eager and CUDA-graph replay."""
+
+import hashlib
+
+import pytest
+import torch
+
+from mlx_batch_invariant_b200.runner import DecoderConfig, GraphedDecoder, ShardedDecoder
+from oracle.reference import bits_of
+
+pytestmark = pytest.mark.gpu
+
+CFG = DecoderConfig(n_layers=3, d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=2048)
+P, STEPS = 70, 5
+
+
+def _run(model, B, graph):
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, CFG.vocab, (1, P), generator=g)
+    gb = torch.Generator().manual_seed(100 + B)
+    rows = torch.randint(0, CFG.vocab, (B, P), generator=gb)
+    rows[0] = prompt[0]
+    rows = rows.cuda()
+    hashes = []
+    model.block_hook = lambda li, h: hashes.append(hashlib.blake2b(bits_of(h[0:1]), digest_size=8).hexdigest())
+    logits = model.forward(rows, 0)
+    model.block_hook = None
+    out = [bits_of(logits[0:1])]
+    if graph:
+        gd = GraphedDecoder(model, B)
+        gd.start(logits.argmax(-1), P)
+        gd.capture()
+        for _ in range(STEPS):
+            out.append(bits_of(gd.step()[0:1].clone()))
+    else:
+        for s in range(STEPS):
+            logits = model.forward(logits.argmax(-1)[:, None], P + s)
+            out.append(bits_of(logits[0:1]))
+    return hashes, out
+
+
+@pytest.mark.parametrize("quant", [None, (4, 64)])
+def test_logits_and_blocks_are_batch_invariant(bi, quant):
+    bi.reset_stats()
+    model = ShardedDecoder(CFG, device="cuda", quant=quant, max_batch=16, max_len=P + STEPS + 1)
+    ref_h, ref_o = _run(model, 1, graph=False)
+    assert len(ref_h) == CFG.n_layers
+    for B in (4, 16):
+        h, o = _run(model, B, graph=False)
+        assert h == ref_h, f"block outputs differ at batch {B}"
+        assert o == ref_o, f"logits differ at batch {B}"
+    h, o = _run(model, 4, graph=True)
+    assert h == ref_h and o == ref_o, "CUDA-graph replay differs from eager decoding"
+    bi.check_device_status()
+
+
+def test_logits_match_float64_semantics(bi):
+    """Tolerance tier for the whole model: the same weights through plain float64 torch ops."""
+    from tests.test_dist_cpu import Float64Backend
+
+    model = ShardedDecoder(CFG, device="cuda", max_batch=2, max_len=P + 2)
+    g = torch.Generator().manual_seed(0)
+    rows = torch.randint(0, CFG.vocab, (2, P), generator=g).cuda()
+    got = model.forward(rows, 0).float().cpu()
+
+    class Cuda64(Float64Backend):
+        def prefill_attention(self, q, k, v, scale):
+            Tq, L = q.shape[2], k.shape[2]
+            m = torch.ones(Tq, L, dtype=torch.bool, device=q.device).tril(L - Tq)
+            return torch.nn.functional.scaled_dot_product_attention(q.double(), k.double(), v.double(), attn_mask=m, scale=scale,
+                                                                    enable_gqa=True).to(q.dtype)
+
+    model.ops = Cuda64()
+    ref = model.forward(rows, 0).float().cpu()
+    rel = float((got - ref).abs().max() / ref.abs().max())
+    assert rel < 5e-2, rel
