@@ -143,6 +143,23 @@ int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int6
                     int64_t kv_sl, float scale, int causal, int split_size, int dtype,
                     void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * Decoder-runner glue. No counterpart in the reference (there mlx_lm's model *
+ * code does this with framework ops). Elementwise, batch-invariant by         *
+ * construction.                                                               *
+ * bi_rope_append: qkv[B*T, (Hq+2*Hkv)*D] as the qkv projection wrote it;       *
+ *   token (b, t) is at position pos0[0] + t (pos0: int64 on the device);       *
+ *   q -> q_out[B, Hq, T, D] rotated with cos/sin tables fp32 [positions, D]    *
+ *   (the two halves of a head share an angle); rotated k and plain v are       *
+ *   written into the caches [*, Hkv, capacity, D] (element strides given).     *
+ * bi_swiglu: out[M, F] = T(silu(gu[:, :F]) * gu[:, F:]) for gu[M, 2F].         *
+ * ------------------------------------------------------------------------ */
+int bi_rope_append(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos0,
+                   void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                   int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int dtype, void* stream);
+
+int bi_swiglu(const void* gate_up, void* out, int64_t M, int64_t F, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

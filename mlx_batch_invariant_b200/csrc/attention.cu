@@ -344,16 +344,13 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
         __syncwarp();                                      // stage st visible; slot of stage st-1 free
         issue(st + DEC2_STAGES - 1);
         const uint8_t* stage = ring + (st % DEC2_STAGES) * C::STAGE_BYTES;
+        // Phase A: scores of every key of the stage (independent of the softmax state, so the
+        // four keys' dot products and shuffle trees overlap). Phase B: the sequential softmax steps.
+        float s[DEC2_KC][GU];
 #pragma unroll
         for (int key = 0; key < DEC2_KC; ++key) {
-            const int jj = st * DEC2_KC + key;
-            if (jj >= nk_max) break;                       // warp-uniform
-            const bool on = jj < nk;
-            uint64_t kp[2][DL], vp[2][DL];
+            uint64_t kp[2][DL];
             load_slice_pairs<T, DL>(stage + (key * 4 + o) * C::PITCH, r, kp);
-            load_slice_pairs<T, DL>(stage + ((DEC2_KC + key) * 4 + o) * C::PITCH, r, vp);
-            // scores of the GU heads: packed fma chains, tree levels 16 and 8 local, 4-2-1 by shuffle
-            float s[GU];
 #pragma unroll
             for (int iq = 0; iq < GU; ++iq) {
                 uint64_t p01 = ptx::pack2(0.0f, 0.0f), p23 = ptx::pack2(0.0f, 0.0f);
@@ -368,12 +365,20 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
                 t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 4));
                 t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
                 t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
-                s[iq] = t;
+                s[key][iq] = t;
             }
-            // softmax step of head `my_head` on this lane
-            float s_own = s[0];
+        }
 #pragma unroll
-            for (int iq = 1; iq < GU; ++iq) if (my_head == iq) s_own = s[iq];
+        for (int key = 0; key < DEC2_KC; ++key) {
+            const int jj = st * DEC2_KC + key;
+            if (jj >= nk_max) break;                       // warp-uniform
+            const bool on = jj < nk;
+            uint64_t vp[2][DL];
+            load_slice_pairs<T, DL>(stage + ((DEC2_KC + key) * 4 + o) * C::PITCH, r, vp);
+            // softmax step of head `my_head` on this lane
+            float s_own = s[key][0];
+#pragma unroll
+            for (int iq = 1; iq < GU; ++iq) if (my_head == iq) s_own = s[key][iq];
             const float m_new = fmaxf(m_own, s_own);
             const float e = expf_canon(-fabsf(sub_rn(s_own, m_own)));
             const bool rises = s_own >= m_own;
@@ -416,6 +421,151 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
                     }
             }
         }
+    }
+}
+
+// ---- decode, one stream per warp: when there are few (batch, kv head, split) streams, the four octets
+// of a warp take four query heads of the SAME stream instead of four streams. The K/V rows are copied
+// into shared memory once per warp and read by all four octets, every lane carries one head's state
+// only (few registers, many resident warps), so short caches no longer leave the GPU waiting on one
+// sequential chain per stream. Arithmetic per head is unchanged.
+constexpr int DECW_KC = 4;
+constexpr int DECW_STAGES = 4;
+constexpr int DECW_WARPS = 4;
+
+template <typename T, int DL> struct DecWCfg {
+    static constexpr int ROWB = 32 * DL * (int)sizeof(T);
+    static constexpr int ROWS = 2 * DECW_KC;                                // (k|v, key)
+    static constexpr int STAGE_BYTES = ROWS * ROWB;
+    static constexpr int WARP_BYTES = DECW_STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = DECW_WARPS * WARP_BYTES;
+};
+
+template <typename T, int DL>
+__global__ void __launch_bounds__(32 * DECW_WARPS) decode_warp_stream_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
+    float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
+    KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    using C = DecWCfg<T, DL>;
+    constexpr int D = 32 * DL;
+    constexpr int SEGS = C::ROWB / 16;
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane & (OCT - 1), o = lane >> 3;
+    uint8_t* ring = dec_smem + wid * C::WARP_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+
+    const long long stream = (long long)blockIdx.x * DECW_WARPS + wid;     // (b, kv head, chunk of 4 heads, split)
+    const long long streams = (long long)B * Hkv * nchunk * nsplit;
+    if (stream >= streams) return;                                           // whole warp
+    long long u = stream;
+    const int sp = (int)(u % nsplit); u /= nsplit;
+    const int chunk = (int)(u % nchunk); u /= nchunk;
+    const int hk = (int)(u % Hkv); u /= Hkv;
+    const int b = (int)u;
+    const int G = Hq / Hkv;
+    const int gcount = min(OCT_PER_WARP, G - chunk * OCT_PER_WARP);
+    const bool head_ok = o < gcount;
+    const int h = hk * G + chunk * OCT_PER_WARP + min(o, gcount - 1);
+    const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+    const int j0 = sp * split;
+    const int nk = j0 < Lb ? (min(Lb, j0 + split) - j0) : 0;               // warp-uniform
+    if (nk == 0) return;
+    const int nstage = (nk + DECW_KC - 1) / DECW_KC;
+    const T* const kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+    const T* const vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+
+    auto issue = [&](int st) {
+        if (st < nstage) {
+            const uint32_t dst0 = ring_s + (uint32_t)(st % DECW_STAGES) * C::STAGE_BYTES;
+#pragma unroll
+            for (int i = lane; i < C::ROWS * SEGS; i += 32) {
+                const int seg = i % SEGS, row = i / SEGS;                    // row = kv * KC + key
+                const int key = row % DECW_KC;
+                const int64_t off = (int64_t)min(st * DECW_KC + key, nk - 1) * lay.sl;
+                const uint8_t* src = reinterpret_cast<const uint8_t*>((row >= DECW_KC ? vb : kb) + off) + seg * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * C::ROWB + seg * 16), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    uint64_t qp[2][DL];
+    {
+        const T* qr = q + ((int64_t)b * Hq + h) * D;
+        float qf[NCHUNK * DL];
+        load_slice<T, DL>(qr, r, qf);
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+            for (int d = 0; d < DL; ++d)
+                qp[jp][d] = ptx::pack2(mul_rn(qf[(2 * jp) * DL + d], scale), mul_rn(qf[(2 * jp + 1) * DL + d], scale));
+    }
+    uint64_t accp[2][DL];
+#pragma unroll
+    for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+        for (int d = 0; d < DL; ++d) accp[jp][d] = ptx::pack2(0.0f, 0.0f);
+    float m_own = -INFINITY, l_own = 0.0f;
+
+    for (int st = 0; st < DECW_STAGES - 1; ++st) issue(st);
+    for (int st = 0; st < nstage; ++st) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(DECW_STAGES - 2) : "memory");
+        __syncwarp();
+        issue(st + DECW_STAGES - 1);
+        const uint8_t* stage = ring + (st % DECW_STAGES) * C::STAGE_BYTES;
+        float s[DECW_KC];
+#pragma unroll
+        for (int key = 0; key < DECW_KC; ++key) {
+            uint64_t kp[2][DL];
+            load_slice_pairs<T, DL>(stage + key * C::ROWB, r, kp);
+            uint64_t p01 = ptx::pack2(0.0f, 0.0f), p23 = ptx::pack2(0.0f, 0.0f);
+#pragma unroll
+            for (int d = 0; d < DL; ++d) {
+                p01 = ptx::fma2_rn(qp[0][d], kp[0][d], p01);
+                p23 = ptx::fma2_rn(qp[1][d], kp[1][d], p23);
+            }
+            float a0, a1;
+            ptx::unpack2(ptx::add2_rn(p01, p23), a0, a1);
+            float t = add_rn(a0, a1);
+            t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 4));
+            t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
+            t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
+            s[key] = t;
+        }
+#pragma unroll
+        for (int key = 0; key < DECW_KC; ++key) {
+            if (st * DECW_KC + key >= nk) break;                            // warp-uniform
+            uint64_t vp[2][DL];
+            load_slice_pairs<T, DL>(stage + (DECW_KC + key) * C::ROWB, r, vp);
+            const float m_new = fmaxf(m_own, s[key]);
+            const float e = expf_canon(-fabsf(sub_rn(s[key], m_own)));
+            const bool rises = s[key] >= m_own;
+            const float corr = rises ? e : 1.0f;
+            const float pw = rises ? 1.0f : e;
+            l_own = fma_rn(l_own, corr, pw);
+            m_own = m_new;
+            const uint64_t c2 = ptx::pack2(corr, corr), p2 = ptx::pack2(pw, pw);
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+                for (int d = 0; d < DL; ++d) accp[jp][d] = ptx::fma2_rn(accp[jp][d], c2, ptx::mul2_rn(p2, vp[jp][d]));
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+
+    if (head_ok) {
+        const int64_t po = ((int64_t)b * Hq + h) * nsplit + sp;
+        if (r == 0) { pm[po] = m_own; pl[po] = l_own; }
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+            for (int d = 0; d < DL; ++d) {
+                float lo, hi;
+                ptx::unpack2(accp[jp][d], lo, hi);
+                pacc[po * D + (r + OCT * (2 * jp)) * DL + d] = lo;
+                pacc[po * D + (r + OCT * (2 * jp + 1)) * DL + d] = hi;
+            }
     }
 }
 
@@ -626,6 +776,25 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
         const int64_t per16 = 16 / (int64_t)sizeof(T);
         const bool rows16 = aligned(k, 16) && aligned(v, 16) && lay.sb % per16 == 0 && lay.sh % per16 == 0 &&
                             lay.sl % per16 == 0 && (32 * DL * sizeof(T)) % 16 == 0;
+        const int nchunk4 = (G + 3) / 4;
+        const int64_t streams = B * Hkv * nchunk4 * nsplit;
+        if (rows16 && streams < 148 * 24) {
+            // few streams: one warp per stream, its octets on different heads
+            using CW = DecWCfg<T, DL>;
+            auto kern = decode_warp_stream_kernel<T, DL>;
+            if (CW::SMEM_BYTES > 40 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CW::SMEM_BYTES);
+                if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));
+            }
+            const int64_t blocksw = (streams + DECW_WARPS - 1) / DECW_WARPS;
+            kern<<<(unsigned)blocksw, 32 * DECW_WARPS, CW::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv,
+                                                                             (int)L, lay, scale, split, nsplit, nchunk4);
+            int rcw = check_launch("bi_attn_decode (warp per stream)");
+            if (rcw) return rcw;
+            const int64_t n2w = BH * D;
+            decode_combine_kernel<T><<<(unsigned)((n2w + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
+            return check_launch("bi_attn_decode combine");
+        }
         if (rows16) {
             using C = Dec2Cfg<T, DL>;
             const int64_t blocks2 = (units + DEC2_WARPS * OCT_PER_WARP - 1) / (DEC2_WARPS * OCT_PER_WARP);

@@ -42,8 +42,52 @@ class DecoderConfig:
 LLAMA3_8B = DecoderConfig()
 
 
-class KernelBackend:
-    """The four batch-invariant ops. Tests of the sharding logic swap in a CPU stand-in."""
+class TorchGlue:
+    """Framework-op versions of the elementwise glue (used by CPU stand-in backends in tests)."""
+
+    def rope_append(self, qkv, cos, sin, pos0, B, T, hq, hkv, D, kc, vc):
+        """qkv[B*T, (hq+2hkv)*D] -> rotated q[B, hq, T, D]; rotated k and v written into the caches at
+        positions pos0 .. pos0+T-1 (pos0: int64 tensor of one element)."""
+        x = qkv.reshape(B, T, hq + 2 * hkv, D).transpose(1, 2)
+        pos = pos0 + torch.arange(T, device=qkv.device)
+        c, s_ = cos.index_select(0, pos)[None, None], sin.index_select(0, pos)[None, None]
+
+        def rot(t):
+            tf = t.float()
+            half = D // 2
+            r = torch.cat([-tf[..., half:], tf[..., :half]], -1)
+            return (tf * c + r * s_).to(t.dtype)
+
+        kc[:B].index_copy_(2, pos, rot(x[:, hq:hq + hkv]))
+        vc[:B].index_copy_(2, pos, x[:, hq + hkv:].contiguous())
+        return rot(x[:, :hq]).contiguous()
+
+    def swiglu(self, gu):
+        f = gu.shape[1] // 2
+        g = gu[:, :f].float()
+        return (g * torch.sigmoid(g) * gu[:, f:].float()).to(gu.dtype)
+
+
+class KernelBackend(TorchGlue):
+    """The four batch-invariant ops plus the two glue kernels. Tests of the sharding logic swap in a CPU stand-in."""
+
+    def rope_append(self, qkv, cos, sin, pos0, B, T, hq, hkv, D, kc, vc):
+        from .. import _lib
+        q = torch.empty(B, hq, T, D, dtype=qkv.dtype, device=qkv.device)
+        qkv = qkv.contiguous()
+        _lib.check(_lib.load().bi_rope_append(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos0.data_ptr(), q.data_ptr(),
+                                              kc.data_ptr(), vc.data_ptr(), B, T, hq, hkv, D, kc.stride(0), kc.stride(1),
+                                              kc.stride(2), _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device)))
+        return q
+
+    def swiglu(self, gu):
+        from .. import _lib
+        M, f2 = gu.shape
+        gu = gu.contiguous()
+        out = torch.empty(M, f2 // 2, dtype=gu.dtype, device=gu.device)
+        _lib.check(_lib.load().bi_swiglu(gu.data_ptr(), out.data_ptr(), M, f2 // 2, _lib.DTYPE_CODE[gu.dtype],
+                                         _lib.stream_ptr(gu.device)))
+        return out
 
     def linear(self, x, w):                      # x[M, K] @ W[N, K]^T
         return K.batch_invariant_matmul(x, w.T)
@@ -158,13 +202,6 @@ class ShardedDecoder:
         dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
-    def _rope(self, x, pos):                       # x[B, H, T, D], pos[T] (long, device)
-        cos, sin = self.cos.index_select(0, pos)[None, None], self.sin.index_select(0, pos)[None, None]
-        xf = x.float()
-        half = x.shape[-1] // 2
-        rot = torch.cat([-xf[..., half:], xf[..., :half]], -1)
-        return (xf * cos + rot * sin).to(x.dtype)
-
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, start: int) -> torch.Tensor:
         """tokens[B, T] continue every sequence at position `start`; returns logits [B, vocab] of the
@@ -173,28 +210,22 @@ class ShardedDecoder:
         B, T = tokens.shape
         M = B * T
         end = start + T
-        pos = torch.arange(start, end, device=self.dev)
+        pos0 = torch.tensor([start], dtype=torch.long, device=self.dev)
         x = self.embed[tokens.reshape(-1)]                                     # [M, d]
         scale = 1.0 / math.sqrt(D)
         for li, L in enumerate(self.layers):
             h = self.ops.rms_norm(x, L["n1"], cfg.eps)
-            qkv = self._lin(h, L["qkv"]).reshape(B, T, self.hq + 2 * self.hkv, D).transpose(1, 2)
-            q = self._rope(qkv[:, :self.hq], pos)
-            k = self._rope(qkv[:, self.hq:self.hq + self.hkv], pos)
-            v = qkv[:, self.hq + self.hkv:]
-            self.kc[li][:B, :, start:end] = k
-            self.vc[li][:B, :, start:end] = v
+            q = self.ops.rope_append(self._lin(h, L["qkv"]), self.cos, self.sin, pos0, B, T, self.hq, self.hkv, D,
+                                     self.kc[li], self.vc[li])
             kk, vv = self.kc[li][:B, :, :end], self.vc[li][:B, :, :end]
             if T == 1:
-                a = self.ops.decode_attention(q.contiguous(), kk, vv, scale)
+                a = self.ops.decode_attention(q, kk, vv, scale)
             else:
-                a = self.ops.prefill_attention(q.contiguous(), kk, vv, scale)
+                a = self.ops.prefill_attention(q, kk, vv, scale)
             a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
             x = x + self._gather(self._lin(a, L["o"]))
             h = self.ops.rms_norm(x, L["n2"], cfg.eps)
-            gu = self._lin(h, L["gu"])
-            f = cfg.ffn // self.world
-            act = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+            act = self.ops.swiglu(self._lin(h, L["gu"]))
             x = x + self._gather(self._lin(self._gather(act), L["down"]))
             if self.block_hook is not None:
                 self.block_hook(li, x.reshape(B, T, -1))
@@ -207,8 +238,8 @@ class GraphedDecoder:
     """Greedy decoding with the whole decode step captured once in a CUDA graph.
 
     Everything that changes from step to step lives on the device -- the position, the per-sequence
-    key counts, the token buffer -- so one captured step is replayed for every token: the K/V rows are
-    written with an index tensor, RoPE gathers its angles by the same index, attention runs over the
+    key counts, the token buffer -- so one captured step is replayed for every token: the RoPE / cache
+    append kernel reads the position from device memory, attention runs over the
     cache capacity with ``kv_lens``, and the argmax feeds the next step's token buffer. The kernels see
     exactly the calls an eager step makes, so logits are bit-identical to ``ShardedDecoder.forward``.
     """
@@ -229,19 +260,12 @@ class GraphedDecoder:
         x = m.embed[self.tokens.reshape(-1)]
         for li, L in enumerate(m.layers):
             h = m.ops.rms_norm(x, L["n1"], cfg.eps)
-            qkv = m._lin(h, L["qkv"]).reshape(B, 1, m.hq + 2 * m.hkv, D).transpose(1, 2)
-            q = m._rope(qkv[:, :m.hq], self.pos)
-            k = m._rope(qkv[:, m.hq:m.hq + m.hkv], self.pos)
-            v = qkv[:, m.hq + m.hkv:]
-            m.kc[li][:B].index_copy_(2, self.pos, k)
-            m.vc[li][:B].index_copy_(2, self.pos, v.contiguous())
-            a = m.ops.decode_attention(q.contiguous(), m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
+            q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
+            a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
             x = x + m._gather(m._lin(a, L["o"]))
             h = m.ops.rms_norm(x, L["n2"], cfg.eps)
-            gu = m._lin(h, L["gu"])
-            f = cfg.ffn // m.world
-            act = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+            act = m.ops.swiglu(m._lin(h, L["gu"]))
             x = x + m._gather(m._lin(m._gather(act), L["down"]))
         h = m.ops.rms_norm(x, m.nf, cfg.eps)
         logits = m._gather(m._lin(h, m.head))

@@ -17,11 +17,12 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 from mlx_batch_invariant_b200.runner import DecoderConfig, ShardedDecoder, greedy_generate  # noqa: E402
+from mlx_batch_invariant_b200.runner.decoder import TorchGlue  # noqa: E402
 
 CFG = DecoderConfig(n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=128, vocab=96)
 
 
-class Float64Backend:
+class Float64Backend(TorchGlue):
     def linear(self, x, w):
         return (x.double() @ w.double().T).to(x.dtype)
 

@@ -77,3 +77,26 @@ def test_logits_match_float64_semantics(bi):
     ref = model.forward(rows, 0).float().cpu()
     rel = float((got - ref).abs().max() / ref.abs().max())
     assert rel < 5e-2, rel
+
+
+def test_glue_kernels_match_framework_formulas(bi):
+    from mlx_batch_invariant_b200.runner.decoder import KernelBackend, TorchGlue
+
+    B, T, hq, hkv, D, cap = 3, 5, 4, 2, 64, 16
+    g = torch.Generator().manual_seed(0)
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        qkv = torch.randn(B * T, (hq + 2 * hkv) * D, generator=g).to(dt).cuda()
+        ang = torch.rand(cap, D // 2, generator=g) * 6.28
+        cos = torch.cat([ang.cos(), ang.cos()], -1).cuda()
+        sin = torch.cat([ang.sin(), ang.sin()], -1).cuda()
+        pos0 = torch.tensor([7], dtype=torch.long, device="cuda")
+        caches = [[torch.zeros(B, hkv, cap, D, dtype=dt, device="cuda") for _ in range(2)] for _ in range(2)]
+        q_ref = TorchGlue().rope_append(qkv, cos, sin, pos0, B, T, hq, hkv, D, *caches[0])
+        q_got = KernelBackend().rope_append(qkv, cos, sin, pos0, B, T, hq, hkv, D, *caches[1])
+        assert torch.equal(q_ref, q_got)
+        assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1])
+        gu = torch.randn(7, 2 * 96, generator=g).to(dt).cuda() * 3
+        ref = TorchGlue().swiglu(gu).float()
+        got = KernelBackend().swiglu(gu).float()
+        assert (ref - got).abs().max() <= 2e-2 * ref.abs().max()
+        assert torch.equal(KernelBackend().swiglu(gu[2:3]), KernelBackend().swiglu(gu)[2:3])
