@@ -86,6 +86,8 @@ struct Params {
     int n_tiles, m_tiles;
     int split;          // 1: split jobs, 0: fused units
     int x_rows;         // rows of the activation TMA box
+    int box3d;          // 1: one TMA box holds a whole chunk (all K steps of a slot) of an operand
+    int smem_bytes;     // dynamic shared memory of the launch
     int x_bytes;        // shared-memory bytes reserved per activation tile
     int ks;             // K steps (of 64) per chunk = per ring slot = per tcgen05.commit
     int load_slots;     // depth of the TMA ring, in chunks
@@ -284,6 +286,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #ifdef BI_TC_PROFILE
     long long waited = 0;
     const long long t_start = clock64();
+    const uint64_t t_start_ns = ptx::globaltimer_ns();
     const Ctl ctl{p.status, abort_flag, &waited};
 #else
     const Ctl ctl{p.status, abort_flag};
@@ -321,7 +324,13 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     if (warp == WARP_TMA) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const uint32_t step_bytes = (uint32_t)p.x_rows * BLOCK_K * 2 + (QBITS ? C::RAW_BYTES : W_TILE_BYTES);
+            // The TMA unit's cost is per instruction (a few hundred cycles each, whatever the box holds), so
+            // with box3d one box brings all K steps of a chunk: the tensor map is a 3-D view
+            // [K/64 blocks][rows][64 elements] whose box lands as consecutive K-step tiles. K steps of the
+            // box that lie beyond K are zero-filled and still count towards the barrier's bytes.
+            const uint32_t xb = (uint32_t)p.x_rows * BLOCK_K * 2;
+            const uint32_t wb = QBITS ? (uint32_t)C::RAW_BYTES : (uint32_t)W_TILE_BYTES;
+            const bool w3d = p.box3d && !QBITS;
             bool ok = true;
             ChunkIter it(p, ub, ue);
             for (; it.valid() && ok; it.next()) {
@@ -329,13 +338,17 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (it.ci >= LS && !wait_done(it.ci - LS, ROLE_TMA)) { ok = false; break; }
                 const int kc = it.ksteps();
                 const uint32_t bar = bar_lfull(l);
-                ptx::mbar_expect_tx(bar, step_bytes * kc);
+                ptx::mbar_expect_tx(bar, xb * (uint32_t)(p.box3d ? KS : kc) + wb * (uint32_t)(w3d ? KS : kc));
                 const int n0 = it.n0(), m0 = it.m0();
-                for (int j = 0; j < kc; ++j) {
-                    const int k0 = it.k0() + j * BLOCK_K;
-                    if (QBITS) ptx::tma_load_2d(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar);
-                    else       ptx::tma_load_2d(w_tile(l, j), &tmap_w, k0, n0, bar);
-                    ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
+                if (w3d) ptx::tma_load_3d(w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar);
+                if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, it.k0() >> 6, bar);
+                if (!w3d || !p.box3d) {
+                    for (int j = 0; j < kc; ++j) {
+                        const int k0 = it.k0() + j * BLOCK_K;
+                        if (QBITS) ptx::tma_load_2d(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar);
+                        else if (!w3d) ptx::tma_load_2d(w_tile(l, j), &tmap_w, k0, n0, bar);
+                        if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
+                    }
                 }
             }
             if (!ok) {
@@ -350,10 +363,20 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else if (warp == WARP_MMA) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp walks the chunks in lockstep (lane 0 polls the barriers and its verdict is
+        // broadcast), so descriptors and addresses are warp-uniform values; one elected lane issues.
+        {
+            auto warp_wait = [&](uint32_t bar, uint32_t parity, int idx) {
+                int r = 1;
+                if (lane == 0) r = wait_bounded(bar, parity, ctl, ROLE_MMA, idx) ? 1 : 0;
+                return __shfl_sync(0xffffffffu, r, 0) != 0;
+            };
             constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BLOCK_M >> 3) << 17) |
-                                       ((uint32_t)(BLOCK_N >> 4) << 24);
+            // The MMA's N is the batch rows that were loaded, rounded up to the 16 the instruction wants
+            // (columns past the loaded rows see whatever follows in the ring and are never read back).
+            const uint32_t mma_n = (uint32_t)((p.x_rows + 15) & ~15);
+            const uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((mma_n >> 3) << 17) |
+                                   ((uint32_t)(BLOCK_N >> 4) << 24);
             int job = -1; bool ok = true;
             uint32_t tmem_d = tmem_base;
 #ifdef BI_TC_PROFILE
@@ -363,12 +386,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (it.first_in_group()) {
                     ++job;
                     const int buf = job & 1;
-                    if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
+                    if (!warp_wait(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, 32 + buf)) { ok = false; break; }
                     tmem_d = tmem_base + (uint32_t)buf * TMEM_ACC1;
                 }
                 const int l = it.l, w = it.w;
                 const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
-                if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
+                if (!warp_wait(ready, QBITS ? it.wph : it.lph, QBITS ? 8 + w : l)) { ok = false; break; }
 #ifdef BI_TC_PROFILE
                 const long long tq0 = clock64();
 #endif
@@ -385,28 +408,34 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
                     const uint64_t db = ptx::smem_desc_sw128(x_tile(l, j));
                     if (kleft >= BLOCK_K) {
-                        if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
-                        else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
+                        if (ptx::elect_one()) {
+                            if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
+                            else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
+                        }
                     } else {
                         const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
-                        for (int kk = 0; kk < nsteps; ++kk)
-                            ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        if (ptx::elect_one()) {
+                            for (int kk = 0; kk < nsteps; ++kk)
+                                ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        }
                     }
+                    __syncwarp();
                 }
 #ifdef BI_TC_PROFILE
                 const long long tq2 = clock64();
 #endif
-                ptx::umma_commit(bar_done(it.d));
+                if (ptx::elect_one()) ptx::umma_commit(bar_done(it.d));
+                __syncwarp();
 #ifdef BI_TC_PROFILE
                 const long long tq3 = clock64();
                 prof_fence += tq1 - tq0; prof_mma += tq2 - tq1; prof_commit += tq3 - tq2;
 #endif
             }
 #ifdef BI_TC_PROFILE
-            if (p.status) {
+            if (p.status && lane == 0) {
                 unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
                 atomicAdd(c + 8, (unsigned long long)prof_fence); atomicAdd(c + 9, (unsigned long long)prof_mma);
                 atomicAdd(c + 10, (unsigned long long)prof_commit);
@@ -545,6 +574,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
             atomicAdd(c + 2 * role, (unsigned long long)waited);
             atomicAdd(c + 2 * role + 1, (unsigned long long)(clock64() - t_start));
+            if (role == 2) { atomicMax(c + 11, (unsigned long long)(clock64() - t_start)); atomicMax(c + 12, (unsigned long long)(ptx::globaltimer_ns() - t_start_ns)); }
         }
     }
 #endif
@@ -588,6 +618,22 @@ int make_map(CUtensorMap* m, CUtensorMapDataType dt, size_t esize, const void* b
     return BI_OK;
 }
 
+// The same tensor seen as [K/64 blocks][rows][64 elements] (needs K % 64 == 0): a box of `depth` blocks lands
+// as `depth` consecutive K-step tiles of box_rows x 128 bytes.
+int make_map3(CUtensorMap* m, CUtensorMapDataType dt, size_t esize, const void* base, uint64_t kblocks, uint64_t rows,
+              uint64_t ld, uint32_t box_rows, uint32_t depth) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(BI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t gdim[3] = {(cuuint64_t)BLOCK_K, rows, kblocks};
+    cuuint64_t gstr[2] = {ld * esize, (cuuint64_t)BLOCK_K * esize};
+    cuuint32_t box[3] = {(cuuint32_t)BLOCK_K, box_rows, depth};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, dt, 3, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(BI_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
+    return BI_OK;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -597,25 +643,31 @@ int sm_count() {
     return cached[dev] > 0 ? cached[dev] : 148;
 }
 
-template <typename T, int QBITS>
-int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, Params p, cudaStream_t st) {
-    using C = Cfg<QBITS>;
-    auto kern = tc_matmul_kernel<T, QBITS>;
-    // Chunk size and ring depths from the shared-memory budget (a launch-shape choice; no arithmetic
-    // depends on it): the largest chunk that still leaves at least two slots in every ring.
+// Chunk size and ring depths from the shared-memory budget (a launch-shape choice; no arithmetic
+// depends on it): the largest chunk that still leaves at least two slots in every ring.
+// raw_bytes: packed codes per K step of a quantized weight tile, 0 for dense weights.
+bool pick_rings(Params& p, int raw_bytes) {
+    const bool quant = raw_bytes != 0;
     const int avail = SMEM_LIMIT - 1024 - BAR_BYTES;
-    p.w_slots = QBITS ? 2 : 0;
+    p.w_slots = quant ? 2 : 0;
     p.ks = 0;
     for (int ks = 4; ks >= 1; ks >>= 1) {
         const int wring = p.w_slots * ks * W_TILE_BYTES;
-        const int slot = ks * (p.x_bytes + (QBITS ? C::RAW_BYTES : W_TILE_BYTES));
+        const int slot = ks * (p.x_bytes + (quant ? raw_bytes : W_TILE_BYTES));
         const int ls = (avail - wring) / slot;
         if (ls >= 2) { p.ks = ks; p.load_slots = ls < MAX_SLOTS ? ls : MAX_SLOTS; break; }
     }
-    if (!p.ks) return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
-    p.w_ring_slots = QBITS ? p.w_slots : p.load_slots;
-    const int smem_bytes = 1024 + BAR_BYTES + p.load_slots * p.ks * (p.x_bytes + C::RAW_BYTES) +
-                           (QBITS ? p.w_slots : p.load_slots) * p.ks * W_TILE_BYTES;
+    if (!p.ks) return false;
+    p.w_ring_slots = quant ? p.w_slots : p.load_slots;
+    p.smem_bytes = 1024 + BAR_BYTES + p.load_slots * p.ks * (p.x_bytes + raw_bytes) +
+                   (quant ? p.w_slots : p.load_slots) * p.ks * W_TILE_BYTES;
+    return true;
+}
+
+template <typename T, int QBITS>
+int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cudaStream_t st) {
+    using C = Cfg<QBITS>;
+    auto kern = tc_matmul_kernel<T, QBITS>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -626,7 +678,7 @@ int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, Params p, cudaStream_
         attr_done[dev] = true;
     }
     const long long grid = p.units < sm_count() ? p.units : sm_count();
-    kern<<<(unsigned)grid, C::THREADS, smem_bytes, st>>>(mw, mx, p);
+    kern<<<(unsigned)grid, C::THREADS, p.smem_bytes, st>>>(mw, mx, p);
     return check_launch("matmul (tensor-core path)");
 }
 
@@ -667,20 +719,31 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     p.x_rows = (int)mr;
     p.x_bytes = ((int)mr * BLOCK_K * 2 + 1023) / 1024 * 1024;
 
+    if (!pick_rings(p, quant ? BLOCK_N * BLOCK_K * q->bits / 8 : 0))
+        return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
+    p.box3d = K % BLOCK_K == 0 ? 1 : 0;
+
     const CUtensorMapDataType dt = dtype == BI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mw, mx;
-    int rc = make_map(&mx, dt, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)x_ld, BLOCK_K, (uint32_t)p.x_rows,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
+    int rc = BI_OK;
+    if (p.box3d) {
+        // A driver that refuses the 3-D view gets the per-K-step boxes instead; the bytes that land are the same.
+        rc = make_map3(&mx, dt, 2, x, (uint64_t)(K / BLOCK_K), (uint64_t)M, (uint64_t)x_ld, (uint32_t)p.x_rows, (uint32_t)p.ks);
+        if (!rc && !quant) rc = make_map3(&mw, dt, 2, w, (uint64_t)(K / BLOCK_K), (uint64_t)N, (uint64_t)w_ld, BLOCK_N, (uint32_t)p.ks);
+        if (rc) p.box3d = 0;
+    }
+    if (!p.box3d) {
+        rc = make_map(&mx, dt, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)x_ld, BLOCK_K, (uint32_t)p.x_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+        if (!quant) rc = make_map(&mw, dt, 2, w, (uint64_t)K, (uint64_t)N, (uint64_t)w_ld, BLOCK_K, BLOCK_N, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
     if (quant) {
         const uint64_t words = (uint64_t)K * q->bits / 32;
         rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, words, (uint64_t)N, words,
                       (uint32_t)(BLOCK_K * q->bits / 32), BLOCK_N, CU_TENSOR_MAP_SWIZZLE_NONE);
-    } else {
-        rc = make_map(&mw, dt, 2, w, (uint64_t)K, (uint64_t)N, (uint64_t)w_ld, BLOCK_K, BLOCK_N,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
     }
-    if (rc) return rc;
 
     if (dtype == BI_BF16) {
         if (!quant) return launch_t<__nv_bfloat16, 0>(mw, mx, p, st);
