@@ -644,7 +644,8 @@ int sm_count() {
 }
 
 // Chunk size and ring depths from the shared-memory budget (a launch-shape choice; no arithmetic
-// depends on it): the largest chunk that still leaves at least two slots in every ring.
+// depends on it): the largest chunk that still leaves at least two slots in every ring. Measured: larger
+// chunks beat deeper rings (each chunk costs the MMA thread one commit and one pass of its loop).
 // raw_bytes: packed codes per K step of a quantized weight tile, 0 for dense weights.
 bool pick_rings(Params& p, int raw_bytes) {
     const bool quant = raw_bytes != 0;
@@ -677,7 +678,13 @@ int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cuda
         if (e != cudaSuccess) return fail(BI_ERR_CUDA, "matmul smem attr: %s", cudaGetErrorString(e));
         attr_done[dev] = true;
     }
-    const long long grid = p.units < sm_count() ? p.units : sm_count();
+    // Units go to CTAs in equal contiguous shares. With only a few units per CTA an uneven share costs a
+    // whole unit on the critical path (224 tiles on 148 CTAs: some take two, the rest idle half the time), so
+    // the grid shrinks to the largest size at which every CTA gets the same count.
+    const long long sms = sm_count();
+    long long grid = p.units < sms ? p.units : sms;
+    const long long waves = (p.units + sms - 1) / sms;
+    if (waves >= 2 && waves <= 4) grid = (p.units + waves - 1) / waves;
     kern<<<(unsigned)grid, C::THREADS, p.smem_bytes, st>>>(mw, mx, p);
     return check_launch("matmul (tensor-core path)");
 }
