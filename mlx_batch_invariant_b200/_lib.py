@@ -43,6 +43,7 @@ SIGNATURES = {
     "bi_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bi_swiglu": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "bi_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int, c_void_p]),
 }

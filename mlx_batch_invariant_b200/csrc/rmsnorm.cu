@@ -8,6 +8,10 @@
 //   out_i = T((x_i * inv) * w_i)          two fp32 multiplies, one rounding
 // How many rows share the launch never enters: a row sees only its own CTA.
 //
+// bi_add_rms_norm is the same kernel with a residual add in front: sum_i = T(x_i + delta_i) (fp32 add, one
+// rounding -- what an elementwise add of two T arrays gives), written out, and the norm runs over the
+// rounded sums exactly as if they had been read back from memory.
+//
 // Data movement is free to differ from the reference: the row is staged in
 // shared memory with 16-byte loads, each thread then walks its stride-256
 // elements there, results are written back in place and leave with 16-byte
@@ -40,9 +44,9 @@ __device__ __forceinline__ float block_tree_sum(float ss, float* red, int t) {
     return red[0];
 }
 
-template <typename T, bool STAGED, bool HAS_W>
-__global__ void __launch_bounds__(TG) rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                      T* __restrict__ out, int D, float eps) {
+template <typename T, bool STAGED, bool HAS_W, bool HAS_RES>
+__global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __restrict__ delta, const T* __restrict__ w,
+                                                      T* sum_out, T* __restrict__ out, int D, float eps) {
     extern __shared__ uint4 stage_raw[];
     __shared__ float red[TG];
     const int t = threadIdx.x;
@@ -54,10 +58,30 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* __restrict__ x, c
     if (STAGED) {
         constexpr int VEC = 16 / sizeof(T);
         const uint4* src = reinterpret_cast<const uint4*>(xr);
-        for (int i = t; i < D / VEC; i += TG) stage_raw[i] = __ldg(src + i);
+        if (HAS_RES) {
+            // x + delta, rounded to T, goes to shared memory for the norm and to sum_out (which may be x)
+            const uint4* dsrc = reinterpret_cast<const uint4*>(delta + row * (size_t)D);
+            uint4* sdst = reinterpret_cast<uint4*>(sum_out + row * (size_t)D);
+            for (int i = t; i < D / VEC; i += TG) {
+                uint4 a = src[i], b = __ldg(dsrc + i);
+                T* av = reinterpret_cast<T*>(&a);
+                const T* bv = reinterpret_cast<const T*>(&b);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) av[j] = Cvt<T>::down(add_rn(Cvt<T>::up(av[j]), Cvt<T>::up(bv[j])));
+                stage_raw[i] = a;
+                sdst[i] = a;
+            }
+        } else {
+            for (int i = t; i < D / VEC; i += TG) stage_raw[i] = __ldg(src + i);
+        }
         __syncthreads();
+    } else if (HAS_RES) {
+        const T* dr = delta + row * (size_t)D;
+        T* sr = sum_out + row * (size_t)D;
+        for (int i = t; i < D; i += TG) sr[i] = Cvt<T>::down(add_rn(Cvt<T>::up(xr[i]), Cvt<T>::up(dr[i])));
+        // each thread reads back only what it wrote
     }
-    const T* xin = STAGED ? xs : xr;
+    const T* xin = STAGED ? xs : (HAS_RES ? sum_out + row * (size_t)D : xr);
 
     float ss = 0.0f;
     for (int i = t; i < D; i += TG) {
@@ -82,16 +106,20 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* __restrict__ x, c
 }
 
 template <typename T>
-int launch(const void* x, const void* w, void* out, int64_t rows, int64_t D, float eps, cudaStream_t st) {
+int launch(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows, int64_t D, float eps,
+           cudaStream_t st) {
     const size_t row_bytes = (size_t)D * sizeof(T);
-    const bool staged = row_bytes % 16 == 0 && row_bytes <= 160 * 1024 && aligned(x, 16) && aligned(out, 16);
+    const bool staged = row_bytes % 16 == 0 && row_bytes <= 160 * 1024 && aligned(x, 16) && aligned(out, 16) &&
+                        (!delta || (aligned(delta, 16) && aligned(sum_out, 16)));
     const T* xp = static_cast<const T*>(x);
+    const T* dp = static_cast<const T*>(delta);
     const T* wp = static_cast<const T*>(w);
+    T* sp = static_cast<T*>(sum_out);
     T* op = static_cast<T*>(out);
     dim3 grid((unsigned)rows), block(TG);
-#define BI_RMS_LAUNCH(ST, HW)                                                                       \
+#define BI_RMS_LAUNCH2(ST, HW, HR)                                                                  \
     do {                                                                                            \
-        auto kern = rms_norm_kernel<T, ST, HW>;                                                     \
+        auto kern = rms_norm_kernel<T, ST, HW, HR>;                                                 \
         size_t smem = ST ? row_bytes : 0;                                                           \
         if (smem > 48 * 1024) {                                                                     \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
@@ -99,12 +127,14 @@ int launch(const void* x, const void* w, void* out, int64_t rows, int64_t D, flo
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "rms_norm smem attr: %s",               \
                                               cudaGetErrorString(e));                               \
         }                                                                                           \
-        kern<<<grid, block, smem, st>>>(xp, wp, op, (int)D, eps);                                   \
+        kern<<<grid, block, smem, st>>>(xp, dp, wp, sp, op, (int)D, eps);                           \
     } while (0)
+#define BI_RMS_LAUNCH(ST, HW) do { if (delta) BI_RMS_LAUNCH2(ST, HW, true); else BI_RMS_LAUNCH2(ST, HW, false); } while (0)
     if (staged) { if (w) BI_RMS_LAUNCH(true, true); else BI_RMS_LAUNCH(true, false); }
     else        { if (w) BI_RMS_LAUNCH(false, true); else BI_RMS_LAUNCH(false, false); }
 #undef BI_RMS_LAUNCH
-    return check_launch("bi_rms_norm");
+#undef BI_RMS_LAUNCH2
+    return check_launch(delta ? "bi_add_rms_norm" : "bi_rms_norm");
 }
 
 }  // namespace
@@ -120,8 +150,25 @@ extern "C" int bi_rms_norm(const void* x, const void* w, void* out, int64_t rows
     if (rows > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_rms_norm: rows=%lld exceeds the grid limit", (long long)rows);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case BI_F32: return launch<float>(x, w, out, rows, D, eps, st);
-        case BI_F16: return launch<__half>(x, w, out, rows, D, eps, st);
-        default:     return launch<__nv_bfloat16>(x, w, out, rows, D, eps, st);
+        case BI_F32: return launch<float>(x, nullptr, w, nullptr, out, rows, D, eps, st);
+        case BI_F16: return launch<__half>(x, nullptr, w, nullptr, out, rows, D, eps, st);
+        default:     return launch<__nv_bfloat16>(x, nullptr, w, nullptr, out, rows, D, eps, st);
+    }
+}
+
+extern "C" int bi_add_rms_norm(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows,
+                               int64_t D, float eps, int dtype, void* stream) {
+    using namespace bi;
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_add_rms_norm: dtype %d", dtype);
+    if (rows < 0 || D <= 0 || D > INT32_MAX) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm: rows=%lld D=%lld", (long long)rows, (long long)D);
+    if (rows == 0) return BI_OK;
+    if (!x || !delta || !sum_out || !out) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm: null pointer");
+    if (out == sum_out || out == x || out == delta) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm: out must not alias x, delta or sum_out");
+    if (rows > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_add_rms_norm: rows=%lld exceeds the grid limit", (long long)rows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case BI_F32: return launch<float>(x, delta, w, sum_out, out, rows, D, eps, st);
+        case BI_F16: return launch<__half>(x, delta, w, sum_out, out, rows, D, eps, st);
+        default:     return launch<__nv_bfloat16>(x, delta, w, sum_out, out, rows, D, eps, st);
     }
 }

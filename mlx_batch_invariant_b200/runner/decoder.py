@@ -67,9 +67,14 @@ class TorchGlue:
         g = gu[:, :f].float()
         return (g * torch.sigmoid(g) * gu[:, f:].float()).to(gu.dtype)
 
+    def add_rms_norm(self, x, delta, w, eps):
+        """Residual add followed by the norm of the sum: returns (x + delta, rms_norm(x + delta))."""
+        s = x + delta
+        return s, self.rms_norm(s, w, eps)
+
 
 class KernelBackend(TorchGlue):
-    """The four batch-invariant ops plus the two glue kernels. Tests of the sharding logic swap in a CPU stand-in."""
+    """The four batch-invariant ops plus the glue kernels. Tests of the sharding logic swap in a CPU stand-in."""
 
     def rope_append(self, qkv, cos, sin, pos0, B, T, hq, hkv, D, kc, vc):
         from .. import _lib
@@ -88,6 +93,15 @@ class KernelBackend(TorchGlue):
         _lib.check(_lib.load().bi_swiglu(gu.data_ptr(), out.data_ptr(), M, f2 // 2, _lib.DTYPE_CODE[gu.dtype],
                                          _lib.stream_ptr(gu.device)))
         return out
+
+    def add_rms_norm(self, x, delta, w, eps):
+        from .. import _lib
+        x, delta = x.contiguous(), delta.contiguous()
+        rows, D = x.shape
+        s, out = torch.empty_like(x), torch.empty_like(x)
+        _lib.check(_lib.load().bi_add_rms_norm(x.data_ptr(), delta.data_ptr(), w.data_ptr(), s.data_ptr(), out.data_ptr(),
+                                               rows, D, float(eps), _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(x.device)))
+        return s, out
 
     def linear(self, x, w):                      # x[M, K] @ W[N, K]^T
         return K.batch_invariant_matmul(x, w.T)
@@ -213,8 +227,8 @@ class ShardedDecoder:
         pos0 = torch.tensor([start], dtype=torch.long, device=self.dev)
         x = self.embed[tokens.reshape(-1)]                                     # [M, d]
         scale = 1.0 / math.sqrt(D)
+        h = self.ops.rms_norm(x, self.layers[0]["n1"], cfg.eps)
         for li, L in enumerate(self.layers):
-            h = self.ops.rms_norm(x, L["n1"], cfg.eps)
             q = self.ops.rope_append(self._lin(h, L["qkv"]), self.cos, self.sin, pos0, B, T, self.hq, self.hkv, D,
                                      self.kc[li], self.vc[li])
             kk, vv = self.kc[li][:B, :, :end], self.vc[li][:B, :, :end]
@@ -223,10 +237,13 @@ class ShardedDecoder:
             else:
                 a = self.ops.prefill_attention(q, kk, vv, scale)
             a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
-            x = x + self._gather(self._lin(a, L["o"]))
-            h = self.ops.rms_norm(x, L["n2"], cfg.eps)
+            x, h = self.ops.add_rms_norm(x, self._gather(self._lin(a, L["o"])), L["n2"], cfg.eps)
             act = self.ops.swiglu(self._lin(h, L["gu"]))
-            x = x + self._gather(self._lin(self._gather(act), L["down"]))
+            delta = self._gather(self._lin(self._gather(act), L["down"]))
+            if li + 1 < len(self.layers):       # the add of this block and the first norm of the next, one launch
+                x, h = self.ops.add_rms_norm(x, delta, self.layers[li + 1]["n1"], cfg.eps)
+            else:
+                x = x + delta
             if self.block_hook is not None:
                 self.block_hook(li, x.reshape(B, T, -1))
         last = x.reshape(B, T, -1)[:, -1]
@@ -258,16 +275,16 @@ class GraphedDecoder:
         m, cfg, B, D = self.m, self.m.cfg, self.B, self.m.cfg.head_dim
         scale = 1.0 / math.sqrt(D)
         x = m.embed[self.tokens.reshape(-1)]
+        h = m.ops.rms_norm(x, m.layers[0]["n1"], cfg.eps)
         for li, L in enumerate(m.layers):
-            h = m.ops.rms_norm(x, L["n1"], cfg.eps)
             q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
             a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
-            x = x + m._gather(m._lin(a, L["o"]))
-            h = m.ops.rms_norm(x, L["n2"], cfg.eps)
+            x, h = m.ops.add_rms_norm(x, m._gather(m._lin(a, L["o"])), L["n2"], cfg.eps)
             act = m.ops.swiglu(m._lin(h, L["gu"]))
-            x = x + m._gather(m._lin(m._gather(act), L["down"]))
-        h = m.ops.rms_norm(x, m.nf, cfg.eps)
+            delta = m._gather(m._lin(m._gather(act), L["down"]))
+            nxt = m.layers[li + 1]["n1"] if li + 1 < len(m.layers) else m.nf
+            x, h = m.ops.add_rms_norm(x, delta, nxt, cfg.eps)
         logits = m._gather(m._lin(h, m.head))
         self.tokens.copy_(logits.argmax(-1, keepdim=True))
         self.pos.add_(1)

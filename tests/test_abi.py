@@ -44,6 +44,9 @@ def test_version_and_error_string():
     (lambda L: L.bi_rms_norm(None, None, None, 4, 8, 1e-5, 7, None), _lib.BI_ERR_UNSUPPORTED),
     (lambda L: L.bi_rms_norm(None, None, None, 4, 8, 1e-5, _lib.BI_BF16, None), _lib.BI_ERR_BAD_ARG),
     (lambda L: L.bi_rms_norm(None, None, None, 0, 8, 1e-5, _lib.BI_BF16, None), _lib.BI_OK),
+    (lambda L: L.bi_add_rms_norm(None, None, None, None, None, 4, 8, 1e-5, 7, None), _lib.BI_ERR_UNSUPPORTED),
+    (lambda L: L.bi_add_rms_norm(None, None, None, None, None, 4, 8, 1e-5, _lib.BI_BF16, None), _lib.BI_ERR_BAD_ARG),
+    (lambda L: L.bi_add_rms_norm(None, None, None, None, None, 0, 8, 1e-5, _lib.BI_BF16, None), _lib.BI_OK),
     (lambda L: L.bi_matmul(None, None, None, None, 0, 4, 4, 4, 4, 1, 1, 4, 9, 0, None, None), _lib.BI_ERR_UNSUPPORTED),
     (lambda L: L.bi_matmul(None, None, None, None, 0, 4, 4, 4, 4, 1, 1, 4, _lib.BI_F32, 0, None, None), _lib.BI_ERR_BAD_ARG),
     (lambda L: L.bi_matmul(None, None, None, None, 0, 0, 4, 4, 4, 1, 1, 4, _lib.BI_F32, 0, None, None), _lib.BI_OK),

@@ -57,3 +57,27 @@ def test_tolerance_vs_float64(bi, dt):
 def test_empty(bi):
     out = bi.batch_invariant_rms_norm(torch.empty(0, 64, device="cuda"), None, 1e-5)
     assert out.shape == (0, 64)
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("rows,D", [(1, 4096), (64, 4096), (5, 100), (3, 257), (2, 50000)])
+def test_add_rms_norm_equals_add_then_norm(bi, dt, rows, D):
+    """The fused residual add + norm gives the bits of an elementwise add followed by the norm kernel
+    (and of the oracle over that sum), staged and unstaged rows, also with the sum written over x."""
+    from mlx_batch_invariant_b200.runner.decoder import KernelBackend
+    g = torch.Generator().manual_seed(rows * 7 + D)
+    x = (3 * torch.randn(rows, D, generator=g)).to(dt)
+    d = torch.randn(rows, D, generator=g).to(dt)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dt)
+    s_ref = x + d
+    s, h = KernelBackend().add_rms_norm(x.cuda(), d.cuda(), w.cuda(), 1e-5)
+    assert R.bits_of(s) == R.bits_of(s_ref)
+    assert R.bits_of(h) == R.bits_of(R.rms_norm(s_ref, w, 1e-5))
+    assert R.bits_of(h) == R.bits_of(bi.batch_invariant_rms_norm(s_ref.cuda(), w.cuda(), 1e-5))
+    # in place: sum_out = x
+    from mlx_batch_invariant_b200 import _lib
+    xg, dg, wg = x.cuda(), d.cuda(), w.cuda()
+    out = torch.empty_like(xg)
+    _lib.check(_lib.load().bi_add_rms_norm(xg.data_ptr(), dg.data_ptr(), wg.data_ptr(), xg.data_ptr(), out.data_ptr(), rows, D,
+                                           1e-5, _lib.DTYPE_CODE[dt], _lib.stream_ptr(xg.device)))
+    assert R.bits_of(xg) == R.bits_of(s_ref) and R.bits_of(out) == R.bits_of(h)
