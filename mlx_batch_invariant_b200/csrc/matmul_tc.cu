@@ -461,20 +461,41 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int ncols = min(BLOCK_M, p.M - m0);
             const uint32_t acc = lane_base + (uint32_t)buf * TMEM_ACC1;
             const bool first = g == 0, last = g == p.G - 1;
+            if (p.split) {
+                // A TMEM load queues behind the MMAs already issued for the next unit, so the loads of two
+                // column blocks go out together and pay that wait once.
 #pragma unroll 1
-            for (int c = 0; c * 32 < ncols; ++c) {  // warp-uniform trip count
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(acc + c * 32, v);
-                if (p.split) {
+                for (int c = 0; c * 32 < ncols; c += 2) {  // warp-uniform trip count
+                    uint32_t v0[32], v1[32];
+                    const bool two = (c + 1) * 32 < ncols;
+                    ptx::tmem_ld_32x32(acc + c * 32, v0);
+                    if (two) ptx::tmem_ld_32x32(acc + c * 32 + 32, v1);
                     ptx::tmem_ld_wait();
+                    if ((c + 2) * 32 >= ncols) {
+                        // the accumulator is in registers: hand it back before the stores go out
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
+                    }
                     if (n < p.N) {
+                        float* dst = p.part + ((long long)g * p.M + m0 + c * 32) * p.N + n;
+                        const int left = p.M - (m0 + c * 32);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int m = m0 + c * 32 + j;
-                            if (m < p.M) p.part[((long long)g * p.M + m) * p.N + n] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j)
+                            if (j < left) dst[(long long)j * p.N] = __uint_as_float(v0[j]);
+                        if (two) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (32 + j < left) dst[(long long)(32 + j) * p.N] = __uint_as_float(v1[j]);
                         }
                     }
-                } else {
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; !p.split && c * 32 < ncols; ++c) {  // warp-uniform trip count
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(acc + c * 32, v);
+                {
                     // fused: the running total lives in TMEM; total = total + p_g, from an exact 0
                     uint32_t t[32];
                     if (!first) ptx::tmem_ld_32x32(lane_base + TMEM_TOTAL + c * 32, t);
@@ -495,10 +516,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                 }
             }
-            if (!p.split && !last) ptx::tmem_st_wait();
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
+            if (!p.split) {
+                if (!last) ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
+            }
         }
     } else if (QBITS && warp >= WARP_DEQ0) {
         // ------------------------------------------------------------ dequantizers
