@@ -331,6 +331,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t xb = (uint32_t)p.x_rows * BLOCK_K * 2;
             const uint32_t wb = QBITS ? (uint32_t)C::RAW_BYTES : (uint32_t)W_TILE_BYTES;
             const bool w3d = p.box3d && !QBITS;
+            // weights are read once per launch: they should not push the batch rows or the split path's
+            // partials out of L2
+            const uint64_t w_policy = ptx::l2_policy_evict_first();
             bool ok = true;
             ChunkIter it(p, ub, ue);
             for (; it.valid() && ok; it.next()) {
@@ -340,13 +343,13 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t bar = bar_lfull(l);
                 ptx::mbar_expect_tx(bar, xb * (uint32_t)(p.box3d ? KS : kc) + wb * (uint32_t)(w3d ? KS : kc));
                 const int n0 = it.n0(), m0 = it.m0();
-                if (w3d) ptx::tma_load_3d(w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar);
+                if (w3d) ptx::tma_load_3d_hint(w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar, w_policy);
                 if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, it.k0() >> 6, bar);
                 if (!w3d || !p.box3d) {
                     for (int j = 0; j < kc; ++j) {
                         const int k0 = it.k0() + j * BLOCK_K;
-                        if (QBITS) ptx::tma_load_2d(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar);
-                        else if (!w3d) ptx::tma_load_2d(w_tile(l, j), &tmap_w, k0, n0, bar);
+                        if (QBITS) ptx::tma_load_2d_hint(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar, w_policy);
+                        else if (!w3d) ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
                         if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
                     }
                 }
