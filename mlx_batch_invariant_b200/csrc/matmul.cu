@@ -8,15 +8,19 @@
 namespace bi {
 namespace {
 
-constexpr int64_t SPLIT_M_MAX = 64;  // above this the raw partials would out-weigh the weight stream
+constexpr int64_t SPLIT_M_MAX = 64;             // up to here the CUDA-core path may split; the tensor-core path always may
+constexpr int64_t SPLIT_PARTIAL_MAX = 80 << 20;  // beyond 64 rows: only while the fp32 partials stay L2-sized
 
 int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 
 // AUTO launch shape for the tensor-core path.
 bool tc_auto_split(int64_t M, int64_t N, int64_t K) {
-    if (ngroups(K) <= 1 || M > SPLIT_M_MAX) return false;
+    if (ngroups(K) <= 1) return false;
     const int64_t tiles = ((N + 127) / 128) * ((M + 127) / 128);
-    return tiles < 148;  // too few tiles to fill the GPU: spread the K groups over CTAs as well
+    if (tiles >= 148) return false;  // enough tiles to fill the GPU without cutting K
+    // too few tiles: spread the K groups over CTAs as well. Measured at N = K = 4096: M = 128 17 us split,
+    // 35 us fused; M = 256 28 us against 35 us; the partials are written and read back through L2.
+    return M <= SPLIT_M_MAX || ngroups(K) * M * N * (int64_t)sizeof(float) <= SPLIT_PARTIAL_MAX;
 }
 // AUTO launch shape for the CUDA-core path (reference rule: M <= 32 and more than one group).
 bool simt_auto_split(int64_t M, int64_t K) { return ngroups(K) > 1 && M <= 32; }
@@ -47,7 +51,8 @@ extern "C" size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     // Enough for whichever shape AUTO may pick; a forced BI_MATMUL_SPLIT always needs
     // ceil(K/256) * M * N * 4 bytes.
-    if (M > SPLIT_M_MAX || ngroups(K) <= 1) return 0;
+    if (ngroups(K) <= 1) return 0;
+    if (M > SPLIT_M_MAX && !tc_auto_split(M, N, K)) return 0;
     return (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
 }
 
