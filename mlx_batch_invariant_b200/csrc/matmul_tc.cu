@@ -331,8 +331,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t xb = (uint32_t)p.x_rows * BLOCK_K * 2;
             const uint32_t wb = QBITS ? (uint32_t)C::RAW_BYTES : (uint32_t)W_TILE_BYTES;
             const bool w3d = p.box3d && !QBITS;
-            // weights are read once per launch: they should not push the batch rows or the split path's
-            // partials out of L2
+            // Weight tiles go through L2 marked evict-first: they should not push the batch rows or the split
+            // path's partials out (measured faster also where several batch tiles re-read a weight tile).
             const uint64_t w_policy = ptx::l2_policy_evict_first();
             bool ok = true;
             ChunkIter it(p, ub, ue);
@@ -366,14 +366,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else if (warp == WARP_MMA) {
         // ------------------------------------------------------------ MMA issuer
-        // The whole warp walks the chunks in lockstep (lane 0 polls the barriers and its verdict is
-        // broadcast), so descriptors and addresses are warp-uniform values; one elected lane issues.
-        {
-            auto warp_wait = [&](uint32_t bar, uint32_t parity, int idx) {
-                int r = 1;
-                if (lane == 0) r = wait_bounded(bar, parity, ctl, ROLE_MMA, idx) ? 1 : 0;
-                return __shfl_sync(0xffffffffu, r, 0) != 0;
-            };
+        if (lane == 0) {
             constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             // The MMA's N is the batch rows that were loaded, rounded up to the 16 the instruction wants
             // (columns past the loaded rows see whatever follows in the ring and are never read back).
@@ -389,12 +382,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (it.first_in_group()) {
                     ++job;
                     const int buf = job & 1;
-                    if (!warp_wait(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, 32 + buf)) { ok = false; break; }
+                    if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
                     tmem_d = tmem_base + (uint32_t)buf * TMEM_ACC1;
                 }
                 const int l = it.l, w = it.w;
                 const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
-                if (!warp_wait(ready, QBITS ? it.wph : it.lph, QBITS ? 8 + w : l)) { ok = false; break; }
+                if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
 #ifdef BI_TC_PROFILE
                 const long long tq0 = clock64();
 #endif
@@ -411,34 +404,28 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
                     const uint64_t db = ptx::smem_desc_sw128(x_tile(l, j));
                     if (kleft >= BLOCK_K) {
-                        if (ptx::elect_one()) {
-                            if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
-                            else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
-                            ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
-                            ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
-                            ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
-                        }
+                        if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
+                        else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
+                        ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
                     } else {
                         const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
-                        if (ptx::elect_one()) {
-                            for (int kk = 0; kk < nsteps; ++kk)
-                                ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
-                        }
+                        for (int kk = 0; kk < nsteps; ++kk)
+                            ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
                     }
-                    __syncwarp();
                 }
 #ifdef BI_TC_PROFILE
                 const long long tq2 = clock64();
 #endif
-                if (ptx::elect_one()) ptx::umma_commit(bar_done(it.d));
-                __syncwarp();
+                ptx::umma_commit(bar_done(it.d));
 #ifdef BI_TC_PROFILE
                 const long long tq3 = clock64();
                 prof_fence += tq1 - tq0; prof_mma += tq2 - tq1; prof_commit += tq3 - tq2;
 #endif
             }
 #ifdef BI_TC_PROFILE
-            if (p.status && lane == 0) {
+            if (p.status) {
                 unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
                 atomicAdd(c + 8, (unsigned long long)prof_fence); atomicAdd(c + 9, (unsigned long long)prof_mma);
                 atomicAdd(c + 10, (unsigned long long)prof_commit);
