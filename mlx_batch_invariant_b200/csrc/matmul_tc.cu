@@ -529,23 +529,62 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int groups_per_row = p.K / p.gs;
         const int per_group = GROUP_K / p.gs;              // 8, 4 or 2 quantization groups per K group
         const int gs_shift = p.gs == 32 ? 5 : (p.gs == 64 ? 6 : 7);
-        constexpr int NQ = GROUP_K / 32;
-        float scv[NQ], bsv[NQ];
+        // Scale / bias entries of one K group (8, 4 or 2 of them), kept as the packed 16-bit words they are
+        // in memory: fetched with one vector load each, a whole K group ahead of their use.
+        const bool sb_vec = (groups_per_row * (int)sizeof(T)) % 16 == 0 && ((uintptr_t)scales % 16) == 0 && ((uintptr_t)biases % 16) == 0;
+        auto fetch = [&](int n, int g, uint32_t (&sw)[4], uint32_t (&bw)[4]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { sw[i] = 0u; bw[i] = 0u; }
+            if (n >= p.N) return;
+            const int q0 = g * per_group;
+            const int have = min(per_group, groups_per_row - q0);
+            const T* sp = scales + (long long)n * groups_per_row + q0;
+            const T* bp = biases + (long long)n * groups_per_row + q0;
+            if (sb_vec && have == per_group) {
+                if (per_group == 8) {
+                    const uint4 a = __ldg(reinterpret_cast<const uint4*>(sp)), b = __ldg(reinterpret_cast<const uint4*>(bp));
+                    sw[0] = a.x; sw[1] = a.y; sw[2] = a.z; sw[3] = a.w; bw[0] = b.x; bw[1] = b.y; bw[2] = b.z; bw[3] = b.w;
+                } else if (per_group == 4) {
+                    const uint2 a = __ldg(reinterpret_cast<const uint2*>(sp)), b = __ldg(reinterpret_cast<const uint2*>(bp));
+                    sw[0] = a.x; sw[1] = a.y; bw[0] = b.x; bw[1] = b.y;
+                } else {
+                    sw[0] = __ldg(reinterpret_cast<const uint32_t*>(sp)); bw[0] = __ldg(reinterpret_cast<const uint32_t*>(bp));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (i < have) {
+                        sw[i >> 1] |= (uint32_t)reinterpret_cast<const unsigned short*>(sp)[i] << (16 * (i & 1));
+                        bw[i >> 1] |= (uint32_t)reinterpret_cast<const unsigned short*>(bp)[i] << (16 * (i & 1));
+                    }
+                }
+            }
+        };
+        auto entry = [&](const uint32_t (&wds)[4], int qi) {   // float(entry qi) of a fetched group
+            uint32_t wd = wds[0];
+            if ((qi >> 1) == 1) wd = wds[1];
+            if ((qi >> 1) == 2) wd = wds[2];
+            if ((qi >> 1) == 3) wd = wds[3];
+            const unsigned short h = (unsigned short)((qi & 1) ? (wd >> 16) : (wd & 0xffffu));
+            T tv;
+            *reinterpret_cast<unsigned short*>(&tv) = h;
+            return Cvt<T>::up(tv);
+        };
+        uint32_t sw[4] = {0u, 0u, 0u, 0u}, bw[4] = {0u, 0u, 0u, 0u};      // current K group
+        uint32_t sw_n[4], bw_n[4];                                        // next K group, in flight
+        {
+            ChunkIter first(p, ub, ue);
+            if (first.valid()) fetch(first.n0() + row, first.g, sw_n, bw_n);
+            else { for (int i = 0; i < 4; ++i) { sw_n[i] = 0u; bw_n[i] = 0u; } }
+        }
         bool ok = true;
         for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
             if (it.first_in_group()) {
-                // scale / bias of every quantization group this K group touches, fetched once per K group
-                const int n = it.n0() + row;
-                const bool live = n < p.N;
-                const int q0 = (it.g * GROUP_K) / p.gs;
-                const long long gi0 = (long long)n * groups_per_row + q0;
-                const int have = min(per_group, groups_per_row - q0);
 #pragma unroll
-                for (int i = 0; i < NQ; ++i) {
-                    const bool on = live && i < have;
-                    scv[i] = on ? Cvt<T>::up(scales[gi0 + i]) : 0.0f;
-                    bsv[i] = on ? Cvt<T>::up(biases[gi0 + i]) : 0.0f;
-                }
+                for (int i = 0; i < 4; ++i) { sw[i] = sw_n[i]; bw[i] = bw_n[i]; }
+                ChunkIter nx(it);
+                do { nx.next(); } while (nx.valid() && !nx.first_in_group());
+                if (nx.valid()) fetch(nx.n0() + row, nx.g, sw_n, bw_n);
             }
             const int l = it.l, w = it.w;
             if (!wait_bounded(bar_lfull(l), it.lph, ctl, ROLE_DEQ, l)) { ok = false; break; }
@@ -553,10 +592,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int kc = it.ksteps();
             for (int j = 0; j < kc; ++j) {
                 const int qi = ((it.c * KS + j) * BLOCK_K + half * 32) >> gs_shift;  // index inside this K group
-                float sc = scv[0], bs = bsv[0];
-#pragma unroll
-                for (int i = 1; i < NQ; ++i)
-                    if (qi == i) { sc = scv[i]; bs = bsv[i]; }
+                const float sc = entry(sw, qi), bs = entry(bw, qi);
                 const uint64_t s2 = ptx::pack2(sc, sc), b2 = ptx::pack2(bs, bs);
                 const uint4* raw = reinterpret_cast<const uint4*>(smem_gen + (raw_tile(l, j) - smem_base) + row * ROW_BYTES + half * (ROW_BYTES / 2));
                 uint32_t rw[HALF_WORDS];
