@@ -167,6 +167,35 @@ int bi_swiglu(const void* gate_up, void* out, int64_t M, int64_t F, int dtype, v
 int bi_add_rms_norm(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows,
                     int64_t D, float eps, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * Feature-slice all-gather over peer memory, for the sharded decoder runner.  *
+ * No counterpart in the reference (single device). Rank r holds               *
+ * local[rows, row_bytes]; after the call every rank's destination holds       *
+ * [rows, world*row_bytes] with rank r's slice in columns                      *
+ * [r*row_bytes, (r+1)*row_bytes). One launch per rank on its own GPU: plain    *
+ * stores into every rank's destination through peer mappings, a system-wide    *
+ * fence, then a flag hand-shake with a bounded wait (2 s; on expiry *status    *
+ * gets 0x20000 | peer << 8 | epoch and the kernel returns). Only bytes move.   *
+ *   dst[world], flags[world]: HOST arrays of device pointers, entry r = rank    *
+ *     r's destination buffer / flag array (uint32[world]) as mapped in THIS      *
+ *     process (own buffers directly, the others through bi_peer_open).           *
+ *   counters: uint32[2] in local device memory, zero before the first call.      *
+ *   Every rank must issue the same sequence of gathers, and rotate over at        *
+ *   least three destination buffers (a peer can be one gather ahead).            *
+ * bi_peer_alloc / bi_peer_free: zero-filled device memory that a CUDA IPC        *
+ *   handle can name (cudaMalloc; the one place the library allocates, at the      *
+ *   caller's explicit request). bi_peer_export: its 64-byte handle, to be sent    *
+ *   to the other ranks' processes; bi_peer_open / bi_peer_close map and unmap     *
+ *   a peer's buffer by handle.                                                   *
+ * ------------------------------------------------------------------------ */
+int bi_peer_alloc(void** ptr, size_t bytes);
+int bi_peer_free(void* ptr);
+int bi_peer_export(void* ptr, uint8_t handle[64]);
+int bi_peer_open(const uint8_t handle[64], void** ptr);
+int bi_peer_close(void* ptr);
+int bi_push_gather(const void* local, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
+                   int64_t row_bytes, int rank, int world, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,13 @@ SIGNATURES = {
     "bi_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bi_swiglu": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "bi_peer_alloc": (c_int, [ctypes.POINTER(c_void_p), c_size_t]),
+    "bi_peer_free": (c_int, [c_void_p]),
+    "bi_peer_export": (c_int, [c_void_p, ctypes.c_char_p]),
+    "bi_peer_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_void_p)]),
+    "bi_peer_close": (c_int, [c_void_p]),
+    "bi_push_gather": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int64, c_int64,
+                               c_int, c_int, c_void_p, c_void_p]),
     "bi_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int, c_void_p]),

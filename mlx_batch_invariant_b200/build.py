@@ -21,7 +21,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libbi_b200.so"
 OBJ = PKG / "build"
-SOURCES = ["abi.cu", "rmsnorm.cu", "attention.cu", "attn_decode_static.cu", "matmul_simt.cu", "matmul_tc.cu", "matmul.cu", "glue.cu"]
+SOURCES = ["abi.cu", "rmsnorm.cu", "attention.cu", "attn_decode_static.cu", "matmul_simt.cu", "matmul_tc.cu", "matmul.cu", "glue.cu", "peer.cu"]
 
 # No fast-math anywhere: IEEE divide / sqrt, denormals kept, and fma contraction off so
 # the only fused operations are the ones the sources spell out.

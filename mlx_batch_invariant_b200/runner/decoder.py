@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import hashlib
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -179,6 +180,7 @@ class ShardedDecoder:
         self.kc = [torch.zeros(max_batch, self.hkv, max_len, D, dtype=dtype, device=self.dev) for _ in range(cfg.n_layers)]
         self.vc = [torch.zeros(max_batch, self.hkv, max_len, D, dtype=dtype, device=self.dev) for _ in range(cfg.n_layers)]
         self.block_hook = None          # callable(layer_index, hidden[B, T, d]) -> None, for per-block hashing
+        self._pg = None                 # peer-memory all-gather, created on first use (world > 1, CUDA)
 
     # ---- weights: every tensor is drawn whole from its own seed, then sliced, so shards of any R agree
     def _gen(self, name):
@@ -210,11 +212,24 @@ class ShardedDecoder:
     def _gather(self, local):
         if self.world == 1:
             return local
-        import torch.distributed as dist
         M, f = local.shape
+        local = local.contiguous()
+        pg = self._push_gather()
+        if pg is not None and pg.fits(M, f * local.element_size()):
+            return pg.gather(local)                      # one launch, result already [M, R*f]
+        import torch.distributed as dist
         buf = torch.empty(self.world * M, f, dtype=local.dtype, device=local.device)
-        dist.all_gather_into_tensor(buf, local.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(buf, local, group=self.group)
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
+
+    def _push_gather(self):
+        """The peer-memory all-gather (CUDA ranks of one node; BI_GATHER=nccl keeps the library collective)."""
+        if self._pg is None and self.dev.type == "cuda" and os.environ.get("BI_GATHER", "push") != "nccl":
+            from .peer import PushGather
+            es = torch.empty(0, dtype=self.dt).element_size()
+            widest = max(self.cfg.vocab, self.cfg.ffn, self.cfg.d_model, self.hq * self.world * self.cfg.head_dim)
+            self._pg = PushGather(self.group, self.rank, self.world, self.dev, self.max_batch * widest * es)
+        return self._pg
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, start: int) -> torch.Tensor:
@@ -300,8 +315,12 @@ class GraphedDecoder:
     def capture(self):
         """Run one eager step (first-call set-up happens outside capture), rewind, then capture."""
         saved = (self.tokens.clone(), self.pos.clone(), self.lens.clone())
+        pg = self.m._push_gather() if self.m.world > 1 else None
+        before = pg.calls if pg is not None else 0
         self._step()
         torch.cuda.synchronize(self.m.dev)
+        if pg is not None:
+            pg.set_cycle(pg.calls - before)     # the captured step's gathers repeat back to back
         for dst, src in zip((self.tokens, self.pos, self.lens), saved):
             dst.copy_(src)
         self.graph = torch.cuda.CUDAGraph()

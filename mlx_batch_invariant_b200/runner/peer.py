@@ -1,0 +1,86 @@
+"""Feature-slice all-gather over peer memory for the sharded decoder (host side of ``bi_push_gather``).
+
+Every rank allocates one block of device memory through the library (``bi_peer_alloc``: a CUDA IPC handle
+can name it), sends the handle to the other ranks over the process group, and maps theirs. A gather is
+then one kernel launch per rank that stores the local slice into every rank's destination and shakes
+hands through flag words (``csrc/peer.cu``); the result is already in ``[rows, world * f]`` order.
+
+Destination buffers rotate: a peer can be one gather ahead of the slowest rank, never two, so three
+buffers are enough in a straight run. A captured CUDA graph replays a fixed sequence of ``n`` gathers;
+the rotation modulus is then chosen so that the last gather of one replay and the first of the next
+use different buffers (``set_cycle``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+
+NBUF = 5          # allocated destinations; 3, 4 or 5 of them are cycled through
+
+
+class _Raw:
+    """A device pointer as something torch.as_tensor can wrap (no copy, no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PushGather:
+    def __init__(self, group, rank: int, world: int, device: torch.device, max_bytes: int):
+        import torch.distributed as dist
+        self.rank, self.world, self.dev = rank, world, device
+        self.lib = _lib.load()
+        self.cap = (max_bytes + 255) // 256 * 256                 # bytes of one gathered destination
+        total = NBUF * self.cap + 256                             # + the flag array (uint32[world])
+        with torch.cuda.device(device):
+            base = ctypes.c_void_p()
+            _lib.check(self.lib.bi_peer_alloc(ctypes.byref(base), total))
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(self.lib.bi_peer_export(base, handle))
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.bases = []
+            for r in range(world):
+                if r == rank:
+                    self.bases.append(base.value)
+                else:
+                    p = ctypes.c_void_p()
+                    _lib.check(self.lib.bi_peer_open(handles[r], ctypes.byref(p)))
+                    self.bases.append(p.value)
+            self.own = [torch.as_tensor(_Raw(base.value + b * self.cap, self.cap), device=device) for b in range(NBUF)]
+            self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        self.calls = 0
+        self.mod = 3
+        dist.barrier(group=group)                                 # every rank has mapped every buffer
+
+    def fits(self, rows: int, row_bytes: int) -> bool:
+        return rows * row_bytes * self.world <= self.cap and row_bytes % 16 == 0
+
+    def set_cycle(self, n: int) -> None:
+        """A sequence of n gathers is about to be replayed back to back: pick the rotation modulus."""
+        prev = (self.calls - 1) % self.mod if self.calls else -1
+        for m in (3, 4, 5):
+            if n % m != 1:
+                self.mod = m
+                self.calls = prev + 1          # the next gather's buffer differs from the last one used
+                return
+        raise RuntimeError(f"no buffer rotation for a cycle of {n} gathers")
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        """local[rows, f] (contiguous) -> [rows, world * f], rank-major along the feature axis."""
+        rows, f = local.shape
+        row_bytes = f * local.element_size()
+        b = self.calls % self.mod
+        self.calls += 1
+        arr = ctypes.c_void_p * self.world
+        dst = arr(*[base + b * self.cap for base in self.bases])
+        flags = arr(*[base + NBUF * self.cap for base in self.bases])
+        status = _lib.status_word(self.dev)
+        _lib.check(self.lib.bi_push_gather(local.data_ptr(), dst, flags, self.counters.data_ptr(), rows, row_bytes,
+                                           self.rank, self.world, status.data_ptr(), _lib.stream_ptr(self.dev)))
+        n = rows * row_bytes * self.world
+        return self.own[b][:n].view(local.dtype).view(rows, self.world * f)

@@ -29,7 +29,7 @@ def _generate(rank, world, quant):
     from mlx_batch_invariant_b200.runner import GraphedDecoder, ShardedDecoder
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    model = ShardedDecoder(_cfg(), rank=rank, world=world, device=dev, quant=quant, max_batch=B, max_len=P + STEPS + 1)
+    model = ShardedDecoder(_cfg(), rank=rank, world=world, device=dev, quant=quant, max_batch=B, max_len=P + STEPS + 2)
     g = torch.Generator().manual_seed(3)
     rows = torch.randint(0, 2048, (B, P), generator=g).to(dev)
     logits = model.forward(rows, 0)
@@ -37,17 +37,26 @@ def _generate(rank, world, quant):
     for s in range(STEPS):
         logits = model.forward(logits.argmax(-1)[:, None], P + s)
         outs.append(logits.cpu())
+    # the same continuation from a captured CUDA graph, replayed (the gathers' buffer rotation repeats)
+    model.forward(rows, 0)
+    gd = GraphedDecoder(model, B)
+    gd.start(outs[0].to(dev).argmax(-1), P)
+    gd.capture()
+    for s in range(STEPS):
+        outs.append(gd.step().clone().cpu())
     return outs
 
 
-def _worker(rank, world, port, quant, out_path):
+def _worker(rank, world, port, quant, out_path, gather="push"):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", BI_GATHER=gather)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         outs = _generate(rank, world, quant)
+        from mlx_batch_invariant_b200 import check_device_status
+        check_device_status(torch.device("cuda", rank))       # no bounded wait of the peer gather ran out
         if rank == 0:
             torch.save(outs, out_path)
         dist.barrier()
@@ -61,14 +70,18 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("gather", ["push", "nccl"])
 @pytest.mark.parametrize("quant", [None, (4, 64)])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_logits_identical_across_gpu_counts(world, quant, tmp_path):
+def test_logits_identical_across_gpu_counts(world, quant, gather, tmp_path):
+    """gather="push": the peer-memory all-gather of csrc/peer.cu; "nccl": the library collective."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    if gather == "nccl" and quant is not None:
+        pytest.skip("the collective's fallback is covered by the dense case")
     ref = _generate(0, 1, quant)
     out = tmp_path / "r0.pt"
-    mp.spawn(_worker, args=(world, _free_port(), quant, str(out)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), quant, str(out), gather), nprocs=world, join=True)
     got = torch.load(out)
     assert len(got) == len(ref)
     for i, (a, b) in enumerate(zip(ref, got)):
