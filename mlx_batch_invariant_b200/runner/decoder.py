@@ -8,7 +8,8 @@ Sharding (R ranks, one process per GPU) uses only dimensions that need no cross-
   * every linear is column-parallel: rank r owns rows [r*N/R, (r+1)*N/R) of W[N, K] and produces
     the matching slice of the output features;
   * attention is sharded by KV head (each rank keeps the cache of its own heads);
-  * the feature slices are joined by all-gather (4 per layer + 1 for the logits).
+  * the feature slices are joined by all-gather (3 per layer + 1 for the logits; the attention output
+    projection is replicated, which is cheaper than a fourth gather).
 Each output element is produced on exactly one GPU by the same K order as on one GPU, so logits are
 bit-identical for every R and every batch size. RMSNorm, RoPE, residual adds, SwiGLU and argmax are
 replicated or elementwise.
@@ -164,7 +165,9 @@ class ShardedDecoder:
             up = self._rows(f"l{li}.up", cfg.ffn, cfg.d_model, cfg.ffn // world)
             self.layers.append(dict(
                 qkv=self._pack(torch.cat([wq, wk, wv], 0)),
-                o=self._pack(self._rows(f"l{li}.wo", cfg.d_model, cfg.n_heads * D, cfg.d_model // world)),
+                # the output projection is kept whole on every rank: at decode sizes streaming all of its
+                # rows costs less than a sharded product plus the all-gather that would have to follow it
+                o=self._pack(self._full(f"l{li}.wo", cfg.d_model, cfg.n_heads * D)),
                 gu=self._pack(torch.cat([gate, up], 0)),
                 down=self._pack(self._rows(f"l{li}.down", cfg.d_model, cfg.ffn, cfg.d_model // world)),
                 n1=self._norm(f"l{li}.n1"), n2=self._norm(f"l{li}.n2")))
@@ -252,7 +255,7 @@ class ShardedDecoder:
             else:
                 a = self.ops.prefill_attention(q, kk, vv, scale)
             a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
-            x, h = self.ops.add_rms_norm(x, self._gather(self._lin(a, L["o"])), L["n2"], cfg.eps)
+            x, h = self.ops.add_rms_norm(x, self._lin(a, L["o"]), L["n2"], cfg.eps)
             act = self.ops.swiglu(self._lin(h, L["gu"]))
             delta = self._gather(self._lin(self._gather(act), L["down"]))
             if li + 1 < len(self.layers):       # the add of this block and the first norm of the next, one launch
@@ -295,7 +298,7 @@ class GraphedDecoder:
             q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
             a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
-            x, h = m.ops.add_rms_norm(x, m._gather(m._lin(a, L["o"])), L["n2"], cfg.eps)
+            x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"]), L["n2"], cfg.eps)
             act = m.ops.swiglu(m._lin(h, L["gu"]))
             delta = m._gather(m._lin(m._gather(act), L["down"]))
             nxt = m.layers[li + 1]["n1"] if li + 1 < len(m.layers) else m.nf

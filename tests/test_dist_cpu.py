@@ -96,8 +96,9 @@ def test_two_rank_sharding_matches_single_rank_quantized(tmp_path):
 def test_shards_are_slices_of_the_full_weights():
     full = _model(0, 1, None)
     parts = [_model(r, 2, None) for r in range(2)]
-    for name in ("o", "down"):
-        assert torch.equal(torch.cat([p.layers[1][name] for p in parts], 0), full.layers[1][name])
+    assert torch.equal(torch.cat([p.layers[1]["down"] for p in parts], 0), full.layers[1]["down"])
+    for p in parts:                                  # the output projection is replicated, not sliced
+        assert torch.equal(p.layers[1]["o"], full.layers[1]["o"])
     assert torch.equal(torch.cat([p.head for p in parts], 0), full.head)
     hq, hkv, D = CFG.n_heads // 2, CFG.n_kv_heads // 2, CFG.head_dim
     fq = full.layers[0]["qkv"]
