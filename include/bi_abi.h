@@ -2,8 +2,9 @@
  * C ABI of the B200 batch-invariant kernel library (libbi_b200.so).
  *
  * Every entry point is a plain C function over raw device pointers, sizes and
- * element strides. The library owns no device memory (one documented exception:
- * bi_attn_decode_static): inputs, outputs and any scratch ("workspace") are
+ * element strides. The library owns no device memory (documented exceptions:
+ * bi_attn_decode_static's built-in array, and bi_peer_alloc, which exists to
+ * allocate): inputs, outputs and any scratch ("workspace") are
  * allocated by the caller; the matching *_workspace_bytes() call says how much
  * scratch an op needs. Launches go to
  * the caller's stream and never synchronise. The return value is a bi_status;
