@@ -43,6 +43,8 @@ class DecoderConfig:
 
 LLAMA3_8B = DecoderConfig()
 
+PUSH_TESTED_WORLDS = (2,)    # world sizes at which the peer-memory all-gather has run on hardware
+
 
 class TorchGlue:
     """Framework-op versions of the elementwise glue (used by CPU stand-in backends in tests)."""
@@ -226,8 +228,13 @@ class ShardedDecoder:
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
     def _push_gather(self):
-        """The peer-memory all-gather (CUDA ranks of one node; BI_GATHER=nccl keeps the library collective)."""
-        if self._pg is None and self.dev.type == "cuda" and os.environ.get("BI_GATHER", "push") != "nccl":
+        """The peer-memory all-gather (CUDA ranks of one node). BI_GATHER=nccl keeps the library collective,
+        BI_GATHER=push asks for the peer gather at any world size; unset, it is used at the world sizes it has
+        been run at on hardware (PUSH_TESTED_WORLDS) and NCCL elsewhere."""
+        if self._pg is None and self.dev.type == "cuda":
+            mode = os.environ.get("BI_GATHER", "")
+            if mode == "nccl" or (mode != "push" and self.world not in PUSH_TESTED_WORLDS):
+                return None
             from .peer import PushGather
             es = torch.empty(0, dtype=self.dt).element_size()
             widest = max(self.cfg.vocab, self.cfg.ffn, self.cfg.d_model, self.hq * self.world * self.cfg.head_dim)

@@ -19,7 +19,20 @@ import torch
 
 from .. import _lib
 
-NBUF = 5          # allocated destinations; 3, 4 or 5 of them are cycled through
+NBUF = 7          # allocated destinations; 3, 4, 5 or 7 of them are cycled through
+
+
+def pick_cycle(n: int, mod: int, calls: int) -> tuple[int, int]:
+    """Rotation (modulus, call counter) for a sequence of n gathers that will be replayed back to back.
+
+    The buffer of call c is c % modulus. The modulus is the smallest of 3, 4, 5, 7 for which the last gather of
+    one replay and the first of the next use different buffers (n % modulus != 1), and the counter is
+    re-based so that the first gather of the sequence does not reuse the buffer of the gather before it."""
+    prev = (calls - 1) % mod if calls else -1
+    for m in (3, 4, 5, 7):
+        if n % m != 1:
+            return m, prev + 1
+    raise RuntimeError(f"no buffer rotation for a cycle of {n} gathers")
 
 
 class _Raw:
@@ -62,13 +75,7 @@ class PushGather:
 
     def set_cycle(self, n: int) -> None:
         """A sequence of n gathers is about to be replayed back to back: pick the rotation modulus."""
-        prev = (self.calls - 1) % self.mod if self.calls else -1
-        for m in (3, 4, 5):
-            if n % m != 1:
-                self.mod = m
-                self.calls = prev + 1          # the next gather's buffer differs from the last one used
-                return
-        raise RuntimeError(f"no buffer rotation for a cycle of {n} gathers")
+        self.mod, self.calls = pick_cycle(n, self.mod, self.calls)
 
     def gather(self, local: torch.Tensor) -> torch.Tensor:
         """local[rows, f] (contiguous) -> [rows, world * f], rank-major along the feature axis."""

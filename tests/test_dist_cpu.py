@@ -120,3 +120,22 @@ def test_world_must_divide_the_sharded_dims():
     import pytest
     with pytest.raises(ValueError):
         ShardedDecoder(CFG, rank=0, world=4, device="cpu", dtype=torch.float32, backend=Float64Backend())
+
+
+def test_peer_gather_buffer_rotation_never_reuses_a_live_buffer():
+    """Replaying a captured sequence of n gathers: consecutive gathers, also across the replay boundary and
+    across the switch from the eager warm-up, must land in different destination buffers."""
+    from mlx_batch_invariant_b200.runner.peer import NBUF, pick_cycle
+    for n in range(2, 400):
+        for warm in (0, 1, 2, 3, 7):
+            last_eager = (warm - 1) % 3 if warm else None
+            mod, calls = pick_cycle(n, 3, warm)
+            assert 3 <= mod <= NBUF
+            seq = [(calls + i) % mod for i in range(n)]
+            if last_eager is not None:
+                assert seq[0] != last_eager
+            replayed = seq + seq
+            assert all(a != b for a, b in zip(replayed, replayed[1:]))
+    import pytest
+    with pytest.raises(RuntimeError):
+        pick_cycle(421, 3, 0)                         # 1 mod 3, 4, 5 and 7: no modulus on offer works
