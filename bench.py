@@ -303,6 +303,13 @@ class RMSNormW(Workload):
         return self.algo_bytes() / dt / 1e9, f"whole [{self.M},{self.D}] input, mean of {reps} passes"
 
 
+# DRAM bytes (read + write) of one launch of the workload's dominant kernel, from the ncu captures
+# summarised under profiles/ (tc_matmul_dense_bf16.md, tc_matmul_qmm4_decode.md,
+# attn_decode_stream_b64_l4096.md); None where no capture of that workload exists.
+NCU_TRAFFIC_BYTES = {
+    "matmul_bf16_m64": 34.17e6, "matmul_bf16_m256": 47.3e6, "qmm4_decode": 33.13e6, "attn_decode": 1.0887e9,
+}
+
 WORKLOADS = {c.name: c for c in (MatmulBF16, MatmulBF16M1, MatmulBF16M64, QMM4Decode, AttnDecode, RMSNormW)}
 
 
@@ -379,11 +386,13 @@ def run_ours(args):
         if wl.bound == "hbm":
             achieved = wl.algo_bytes() / per / 1e9
             roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": f"of {pk['which']}"}
+                    "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                    "peak_source": f"of {pk['which']}"}
         else:
             achieved = wl.flops() / per / 1e12
             roof = {"bound": "tensor", "achieved": round(achieved, 1), "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": round(achieved / pk["bf16_tflops"], 4), "traffic": None, "peak_source": f"of {pk['which']}"}
+                    "frac": round(achieved / pk["bf16_tflops"], 4), "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                    "peak_source": f"of {pk['which']}"}
         from oracle import reference as R
         cores = os.cpu_count() or 1
         cv, sample = wl.cpu_sample(R, cores) if world == 1 or True else (None, "")
