@@ -12,6 +12,7 @@ Prints ONE JSON line (rank 0). Workloads:
     matmul_bf16_m256   dense y = x @ W^T, x[256,4096], W[4096,4096], bf16     -> TFLOP/s
     qmm4_decode        4-bit group-64 quantized matmul, M=1, K=4096 -> N=14336  -> GB/s
     attn_decode        decode attention, bf16, 32/8 heads, D=128, B=64, L=4096  -> GB/s
+    attn_decode_short  the same at the decoder workload's shape: 560 keys in a 640-key cache -> GB/s
     rms_norm           RMSNorm [256,4096] bf16                                  -> GB/s
 
 Timing: CUDA events on the launching stream, W >= 3 warm-up steps, inputs rotated over more
@@ -132,7 +133,7 @@ class MatmulBF16(Workload):
         self.x_host = torch.randn(self.M, self.K, generator=g).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(dev)
         self.y_host = torch.empty(self.M, self.N, dtype=torch.bfloat16).pin_memory()
-        self.launches_per_step = 1                        # fused path at M=256
+        self.launches_per_step = 2                        # split kernel + combine (AUTO splits up to M = 256 here)
 
     def step(self, i):
         return self.bi.batch_invariant_matmul(self.x, self.W[i % self.nbuf].T)
@@ -266,6 +267,44 @@ class AttnDecode(Workload):
         return nb * (2.0 * self.Hkv * self.L * self.D * 2) / dt / 1e9, f"{nb} of {self.B} sequences, {dt:.1f} s"
 
 
+class AttnDecodeShort(AttnDecode):
+    """Decode attention at the shape of the decoder workload: 64 sequences of 560 keys in a 640-key cache."""
+    name, metric = "attn_decode_short", "decode attention HBM GB/s"
+    L, KEYS = 640, 560
+
+    def __init__(self, torch, bi, dev):
+        super().__init__(torch, bi, dev)
+        self.nbuf = 4                                       # 4 x 168 MB of K/V > L2
+        g = torch.Generator(device=dev).manual_seed(1)
+        while len(self.k) < self.nbuf:
+            self.k.append(torch.randn(self.B, self.Hkv, self.L, self.D, generator=g, device=dev, dtype=torch.bfloat16))
+            self.v.append(torch.randn(self.B, self.Hkv, self.L, self.D, generator=g, device=dev, dtype=torch.bfloat16))
+        self.lens = torch.full((self.B,), self.KEYS, dtype=torch.int32, device=dev)
+
+    def step(self, i):
+        j = i % self.nbuf
+        return self.bi.batch_invariant_decode_attention(self.q, self.k[j], self.v[j], scale=self.D ** -0.5, kv_lens=self.lens)
+
+    def step_e2e(self, i):
+        j = i % self.nbuf
+        q = self.q_host.to(self.dev, non_blocking=True)
+        o = self.bi.batch_invariant_decode_attention(q, self.k[j], self.v[j], scale=self.D ** -0.5, kv_lens=self.lens)
+        self.o_host.copy_(o, non_blocking=True)
+        return self.q_host.numel() * 2, self.o_host.numel() * 2
+
+    def algo_bytes(self): return self.B * (2.0 * self.Hkv * self.KEYS * self.D * 2 + 2.0 * self.Hq * self.D * 2)
+    def config(self):
+        return {"workload": self.name, "B": self.B, "Hq": self.Hq, "Hkv": self.Hkv, "L": self.L, "keys": self.KEYS, "D": self.D,
+                "l2": "four K/V sets of 168 MB rotated"}
+
+    def cpu_sample(self, R, threads):
+        q, k, v = self.q_host[:1].clone(), self.k[0][:1, :, :self.KEYS].cpu().contiguous(), self.v[0][:1, :, :self.KEYS].cpu().contiguous()
+        t0 = time.perf_counter()
+        R.attn_decode(q, k, v, scale=self.D ** -0.5)
+        dt = time.perf_counter() - t0
+        return (2.0 * self.Hkv * self.KEYS * self.D * 2) / dt / 1e9, f"1 of {self.B} sequences, {dt:.1f} s"
+
+
 class RMSNormW(Workload):
     name, metric, unit, dtype = "rms_norm", "RMSNorm HBM GB/s", "GB/s", "bf16"
     M, D = 256, 4096
@@ -310,7 +349,7 @@ NCU_TRAFFIC_BYTES = {
     "matmul_bf16_m64": 34.17e6, "matmul_bf16_m256": 47.3e6, "qmm4_decode": 33.13e6, "attn_decode": 1.0887e9,
 }
 
-WORKLOADS = {c.name: c for c in (MatmulBF16, MatmulBF16M1, MatmulBF16M64, QMM4Decode, AttnDecode, RMSNormW)}
+WORKLOADS = {c.name: c for c in (MatmulBF16, MatmulBF16M1, MatmulBF16M64, QMM4Decode, AttnDecode, AttnDecodeShort, RMSNormW)}
 
 
 # ---------------------------------------------------------------------------------------------
