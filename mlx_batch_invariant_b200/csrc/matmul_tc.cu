@@ -727,13 +727,13 @@ int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cuda
         if (e != cudaSuccess) return fail(BI_ERR_CUDA, "matmul smem attr: %s", cudaGetErrorString(e));
         attr_done[dev] = true;
     }
-    // Units go to CTAs in equal contiguous shares. With only a few units per CTA an uneven share costs a
+    // Units go to CTAs in equal contiguous shares. With few units per CTA an uneven share costs a
     // whole unit on the critical path (224 tiles on 148 CTAs: some take two, the rest idle half the time), so
     // the grid shrinks to the largest size at which every CTA gets the same count.
     const long long sms = sm_count();
     long long grid = p.units < sms ? p.units : sms;
     const long long waves = (p.units + sms - 1) / sms;
-    if (waves >= 2 && waves <= 4) grid = (p.units + waves - 1) / waves;
+    if (waves >= 2 && waves <= 16) grid = (p.units + waves - 1) / waves;
     kern<<<(unsigned)grid, C::THREADS, p.smem_bytes, st>>>(mw, mx, p);
     return check_launch("matmul (tensor-core path)");
 }
