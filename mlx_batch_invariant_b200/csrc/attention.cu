@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
 // sequential chain per stream. Arithmetic per head is unchanged.
 constexpr int DECW_KC = 4;
 constexpr int DECW_STAGES = 4;
-constexpr int DECW_WARPS = 4;
+constexpr int DECW_WARPS = 16;   // most warps a CTA may have; the launch picks the count (see launch_decode)
 
 template <typename T, int DL> struct DecWCfg {
     static constexpr int ROWB = 32 * DL * (int)sizeof(T);
@@ -441,8 +441,8 @@ template <typename T, int DL> struct DecWCfg {
     static constexpr int SMEM_BYTES = DECW_WARPS * WARP_BYTES;
 };
 
-template <typename T, int DL>
-__global__ void __launch_bounds__(32 * DECW_WARPS) decode_warp_stream_kernel(
+template <typename T, int DL, int MAXW>
+__global__ void __launch_bounds__(32 * MAXW) decode_warp_stream_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
     float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
@@ -455,7 +455,7 @@ __global__ void __launch_bounds__(32 * DECW_WARPS) decode_warp_stream_kernel(
     uint8_t* ring = dec_smem + wid * C::WARP_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
 
-    const long long stream = (long long)blockIdx.x * DECW_WARPS + wid;     // (b, kv head, chunk of 4 heads, split)
+    const long long stream = (long long)blockIdx.x * (blockDim.x >> 5) + wid; // (b, kv head, chunk of 4 heads, split)
     const long long streams = (long long)B * Hkv * nchunk * nsplit;
     if (stream >= streams) return;                                           // whole warp
     long long u = stream;
@@ -781,14 +781,40 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
         if (rows16 && streams < 148 * 24) {
             // few streams: one warp per stream, its octets on different heads
             using CW = DecWCfg<T, DL>;
-            auto kern = decode_warp_stream_kernel<T, DL>;
-            if (CW::SMEM_BYTES > 40 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CW::SMEM_BYTES);
-                if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));
+            // Warps per CTA: the streams are dealt out so that every SM gets the same number of warps (CTAs land
+            // on SMs whole; with a fixed four warps per CTA, 1536 streams put 8 warps on some SMs and 12 on others
+            // and the kernel ran as long as the 12): k CTAs per SM, ceil(streams / (148 k)) warps each. The kernel
+            // is instantiated for CTAs of up to 4, 12 and 16 warps so that the register budget fits the count.
+            constexpr int SMEM_CAP = 200 * 1024;
+            constexpr int MAXW = (SMEM_CAP / CW::WARP_BYTES) < DECW_WARPS ? (SMEM_CAP / CW::WARP_BYTES) : DECW_WARPS;
+            int wpc = 1;
+            for (int k = 1; k <= 64; ++k) {
+                wpc = (int)((streams + 148LL * k - 1) / (148LL * k));
+                if (wpc <= MAXW) break;
             }
-            const int64_t blocksw = (streams + DECW_WARPS - 1) / DECW_WARPS;
-            kern<<<(unsigned)blocksw, 32 * DECW_WARPS, CW::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv,
-                                                                             (int)L, lay, scale, split, nsplit, nchunk4);
+            if (wpc > MAXW) wpc = MAXW;
+            // Below nine warps per SM a warp runs alone on its scheduler most of the time and the 4-warp
+            // instantiation (more registers, more loads in flight per warp) is the faster code: measured 55 us
+            // against 64 us at 768 streams, 40 against 54 us at 32.
+            if (wpc < 9) wpc = 4;
+            const size_t smem_w = (size_t)wpc * CW::WARP_BYTES;
+            const int64_t blocksw = (streams + wpc - 1) / wpc;
+#define BI_DECW_LAUNCH(MW)                                                                                              \
+    do {                                                                                                                \
+        auto kern = decode_warp_stream_kernel<T, DL, MW>;                                                               \
+        static bool attr_set = false; /* per instantiation */                                                           \
+        if (!attr_set && MW * CW::WARP_BYTES > 40 * 1024) {                                                             \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MW * CW::WARP_BYTES); \
+            if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
+            attr_set = true;                                                                                            \
+        }                                                                                                               \
+        kern<<<(unsigned)blocksw, 32 * wpc, smem_w, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv, \
+                                                          (int)L, lay, scale, split, nsplit, nchunk4);                  \
+    } while (0)
+            if (wpc <= 4) BI_DECW_LAUNCH(4);
+            else if (wpc <= 12) { if constexpr (MAXW >= 12) BI_DECW_LAUNCH(12); }
+            else { if constexpr (MAXW >= 16) BI_DECW_LAUNCH(16); }
+#undef BI_DECW_LAUNCH
             int rcw = check_launch("bi_attn_decode (warp per stream)");
             if (rcw) return rcw;
             const int64_t n2w = BH * D;
