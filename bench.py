@@ -342,9 +342,8 @@ class RMSNormW(Workload):
         return self.algo_bytes() / dt / 1e9, f"whole [{self.M},{self.D}] input, mean of {reps} passes"
 
 
-# DRAM bytes (read + write) of one launch of the workload's dominant kernel, from the ncu captures
-# summarised under profiles/ (tc_matmul_dense_bf16.md, tc_matmul_qmm4_decode.md,
-# attn_decode_stream_b64_l4096.md); None where no capture of that workload exists.
+# DRAM bytes (read + write) of one launch of the workload's dominant kernel, from `ncu --set full` captures of
+# these workloads on a B200 (dram__bytes_read.sum + dram__bytes_write.sum); None where no capture exists.
 NCU_TRAFFIC_BYTES = {
     "matmul_bf16_m64": 34.17e6, "matmul_bf16_m256": 47.3e6, "qmm4_decode": 33.13e6, "attn_decode": 1.0887e9,
 }
