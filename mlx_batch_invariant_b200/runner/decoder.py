@@ -43,7 +43,7 @@ class DecoderConfig:
 
 LLAMA3_8B = DecoderConfig()
 
-PUSH_TESTED_WORLDS = (2,)    # world sizes at which the peer-memory all-gather has run on hardware
+PUSH_TESTED_WORLDS = (2, 4)  # world sizes at which the peer-memory all-gather has run on hardware
 
 
 class TorchGlue:
