@@ -69,10 +69,28 @@ int bi_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t D
  * replaces batch_invariant_matmul / launch_tiled / bi_matmul_* /            *
  * bi_matmul_combine (mlx_batch_invariant/kernels/matmul.py:226-234,         *
  * 279-340). Strides are in elements. out is [M, N] contiguous.              *
- * `path` (BI_MATMUL_*) picks the launch shape; AUTO chooses by M. Every     *
- * path gives the same bits.                                                 *
+ * `path` picks the launch shape; AUTO chooses by M, N and K. Every choice   *
+ * gives the same bits. The low byte is one of BI_MATMUL_AUTO / SPLIT (one   *
+ * work unit per K group, fp32 partials in the workspace, a second kernel    *
+ * folds them) / FUSED (one unit folds all groups of a tile in place) /      *
+ * SPLIT_FOLD (split, but the CTA that finishes a tile last folds it: one    *
+ * launch). Optional, ORed in:                                               *
+ *   BI_MATMUL_WS_ZEROED      the first BI_MATMUL_COUNTER_BYTES of the       *
+ *                            workspace are zero when the call starts; the   *
+ *                            call leaves them zero (unless a device wait    *
+ *                            ran out: zero them again then). The partials   *
+ *                            follow that block. Lets AUTO use SPLIT_FOLD.   *
+ *   BI_MATMUL_BATCH_TILE(n)  batch rows per tile: 16, 32, 64 or 128         *
+ *   BI_QMM_STAGE_SMEM/_TMEM  bi_qmm only: stage the dequantized weight in   *
+ *                            shared memory (tile body) or in tensor memory  *
+ *                            (streaming; batch tiles of at most 64 rows)    *
  * ------------------------------------------------------------------------ */
-enum { BI_MATMUL_AUTO = 0, BI_MATMUL_SPLIT = 1, BI_MATMUL_FUSED = 2 };
+enum { BI_MATMUL_AUTO = 0, BI_MATMUL_SPLIT = 1, BI_MATMUL_FUSED = 2, BI_MATMUL_SPLIT_FOLD = 3 };
+#define BI_MATMUL_WS_ZEROED 0x100
+#define BI_MATMUL_BATCH_TILE(n) ((n) << 16)
+#define BI_QMM_STAGE_SMEM 0x1000000
+#define BI_QMM_STAGE_TMEM 0x2000000
+#define BI_MATMUL_COUNTER_BYTES 16384
 
 size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
 

@@ -18,7 +18,14 @@ LIB_PATH = Path(__file__).resolve().parent / "libbi_b200.so"
 BI_OK = 0
 BI_ERR_UNSUPPORTED, BI_ERR_BAD_ARG, BI_ERR_MISALIGNED, BI_ERR_WORKSPACE, BI_ERR_CUDA, BI_ERR_DEVICE_WAIT = 1, 2, 3, 4, 5, 6
 BI_F32, BI_F16, BI_BF16 = 0, 1, 2
-PATH_AUTO, PATH_SPLIT, PATH_FUSED = 0, 1, 2
+PATH_AUTO, PATH_SPLIT, PATH_FUSED, PATH_SPLIT_FOLD = 0, 1, 2, 3
+WS_ZEROED = 0x100                 # BI_MATMUL_WS_ZEROED
+QMM_STAGE_SMEM, QMM_STAGE_TMEM = 0x1000000, 0x2000000
+COUNTER_BYTES = 16384             # BI_MATMUL_COUNTER_BYTES
+
+
+def batch_tile(n: int) -> int:    # BI_MATMUL_BATCH_TILE(n)
+    return n << 16
 
 DTYPE_CODE = {torch.float32: BI_F32, torch.float16: BI_F16, torch.bfloat16: BI_BF16}
 
@@ -118,6 +125,24 @@ def status_word(device: torch.device) -> torch.Tensor:
     return t
 
 
+# Matmul workspaces: one per (device, stream), kept between calls. Its first COUNTER_BYTES are the per-tile
+# arrival counters of the split path's in-kernel fold; they are zero between calls (the kernel leaves them so),
+# which is what the WS_ZEROED flag promises the library. Calls on one stream are ordered, so they can share it.
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def matmul_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A zero-headed workspace of at least `nbytes` for the current stream of `device`."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    need = max(nbytes, COUNTER_BYTES)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        _workspaces[key] = ws
+    return ws
+
+
 def check_device_status(device: torch.device | None = None) -> None:
     """Synchronise and raise if any kernel on `device` gave up a bounded wait."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
@@ -127,4 +152,5 @@ def check_device_status(device: torch.device | None = None) -> None:
     if code != BI_OK:
         msg = last_error()
         word.zero_()
+        _workspaces.clear()          # a kernel that gave up may have left arrival counters behind
         raise KernelError(code, msg)

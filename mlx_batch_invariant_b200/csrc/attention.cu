@@ -368,6 +368,24 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
                 s[key][iq] = t;
             }
         }
+        // Softmax scalars of head `my_head` for every key of the stage, off the serial chain (see
+        // decode_warp_stream_kernel): prefix maximum first, then independent exponentials.
+        float e_own[DEC2_KC];
+        bool rises_own[DEC2_KC];
+        {
+            const bool mine = my_head < gcount;
+            float mrun = m_own;
+#pragma unroll
+            for (int key = 0; key < DEC2_KC; ++key) {
+                float s_own = s[key][0];
+#pragma unroll
+                for (int iq = 1; iq < GU; ++iq) if (my_head == iq) s_own = s[key][iq];
+                e_own[key] = expf_canon(-fabsf(sub_rn(s_own, mrun)));
+                rises_own[key] = s_own >= mrun;
+                if (mine && st * DEC2_KC + key < nk) mrun = fmaxf(mrun, s_own);
+            }
+            m_own = mrun;
+        }
 #pragma unroll
         for (int key = 0; key < DEC2_KC; ++key) {
             const int jj = st * DEC2_KC + key;
@@ -375,17 +393,9 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
             const bool on = jj < nk;
             uint64_t vp[2][DL];
             load_slice_pairs<T, DL>(stage + ((DEC2_KC + key) * 4 + o) * C::PITCH, r, vp);
-            // softmax step of head `my_head` on this lane
-            float s_own = s[key][0];
-#pragma unroll
-            for (int iq = 1; iq < GU; ++iq) if (my_head == iq) s_own = s[key][iq];
-            const float m_new = fmaxf(m_own, s_own);
-            const float e = expf_canon(-fabsf(sub_rn(s_own, m_own)));
-            const bool rises = s_own >= m_own;
-            const float corr_own = rises ? e : 1.0f;
-            const float p_own = rises ? 1.0f : e;
-            const bool upd = on && my_head < gcount;
-            if (upd) { l_own = fma_rn(l_own, corr_own, p_own); m_own = m_new; }
+            const float corr_own = rises_own[key] ? e_own[key] : 1.0f;
+            const float p_own = rises_own[key] ? 1.0f : e_own[key];
+            if (on && my_head < gcount) l_own = fma_rn(l_own, corr_own, p_own);
 #pragma unroll
             for (int iq = 0; iq < GU; ++iq) {
                 const int src = (lane & 24) | iq;
@@ -429,8 +439,8 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
 // into shared memory once per warp and read by all four octets, every lane carries one head's state
 // only (few registers, many resident warps), so short caches no longer leave the GPU waiting on one
 // sequential chain per stream. Arithmetic per head is unchanged.
-constexpr int DECW_KC = 4;
-constexpr int DECW_STAGES = 4;
+constexpr int DECW_KC = 8;
+constexpr int DECW_STAGES = 3;
 constexpr int DECW_WARPS = 16;   // most warps a CTA may have; the launch picks the count (see launch_decode)
 
 template <typename T, int DL> struct DecWCfg {
@@ -533,18 +543,31 @@ __global__ void __launch_bounds__(32 * MAXW) decode_warp_stream_kernel(
             t = add_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
             s[key] = t;
         }
+        // Softmax scalars of the stage, off the serial chain: the running maximum before key j is a prefix
+        // maximum of scores that are already known (max is exact, so evaluating it ahead changes no bit),
+        // and with it every key's exp(-|s_j - m_j|) is independent of the others. What stays sequential
+        // per key is l = fma(l, corr, p) and acc = fma(acc, corr, p * v): the same operations on the same
+        // operands in the same order as the key-by-key form.
+        float e[DECW_KC];
+        bool rises[DECW_KC];
+        {
+            float mrun = m_own;
+#pragma unroll
+            for (int key = 0; key < DECW_KC; ++key) {
+                e[key] = expf_canon(-fabsf(sub_rn(s[key], mrun)));
+                rises[key] = s[key] >= mrun;
+                if (st * DECW_KC + key < nk) mrun = fmaxf(mrun, s[key]);   // warp-uniform predicate
+            }
+            m_own = mrun;
+        }
 #pragma unroll
         for (int key = 0; key < DECW_KC; ++key) {
             if (st * DECW_KC + key >= nk) break;                            // warp-uniform
             uint64_t vp[2][DL];
             load_slice_pairs<T, DL>(stage + (DECW_KC + key) * C::ROWB, r, vp);
-            const float m_new = fmaxf(m_own, s[key]);
-            const float e = expf_canon(-fabsf(sub_rn(s[key], m_own)));
-            const bool rises = s[key] >= m_own;
-            const float corr = rises ? e : 1.0f;
-            const float pw = rises ? 1.0f : e;
+            const float corr = rises[key] ? e[key] : 1.0f;
+            const float pw = rises[key] ? 1.0f : e[key];
             l_own = fma_rn(l_own, corr, pw);
-            m_own = m_new;
             const uint64_t c2 = ptx::pack2(corr, corr), p2 = ptx::pack2(pw, pw);
 #pragma unroll
             for (int jp = 0; jp < 2; ++jp)

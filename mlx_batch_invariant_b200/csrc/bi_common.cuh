@@ -25,6 +25,17 @@ inline size_t dtype_size(int dtype) { return dtype == BI_F32 ? 4 : 2; }
 
 inline bool dtype_ok(int dtype) { return dtype == BI_F32 || dtype == BI_F16 || dtype == BI_BF16; }
 
+// Streaming multiprocessors of the current device (cached per device ordinal). Launch shapes are
+// sized from it; no arithmetic depends on it.
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+
 // Canonical constants of the arithmetic contract.
 constexpr int GROUP_K = 256;  // K is folded in groups of this many elements, whatever M is
 

@@ -10,35 +10,93 @@ namespace {
 
 constexpr int64_t SPLIT_M_MAX = 64;             // up to here the CUDA-core path may split; the tensor-core path always may
 constexpr int64_t SPLIT_PARTIAL_MAX = 80 << 20;  // beyond 64 rows: only while the fp32 partials stay L2-sized
+constexpr int64_t FOLD_M_MAX = 16;              // in-kernel fold of the split path: the last CTA of a tile reads G * M * 128 partials
+constexpr size_t COUNTER_BYTES = BI_MATMUL_COUNTER_BYTES;
 
 int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 
-// AUTO launch shape for the tensor-core path.
-bool tc_auto_split(int64_t M, int64_t N, int64_t K) {
-    if (ngroups(K) <= 1) return false;
-    const int64_t tiles = ((N + 127) / 128) * ((M + 127) / 128);
-    if (tiles >= 148) return false;  // enough tiles to fill the GPU without cutting K
-    // too few tiles: spread the K groups over CTAs as well. Measured at N = K = 4096: M = 128 17 us split,
-    // 35 us fused; M = 256 28 us against 35 us; the partials are written and read back through L2.
-    return M <= SPLIT_M_MAX || ngroups(K) * M * N * (int64_t)sizeof(float) <= SPLIT_PARTIAL_MAX;
+// AUTO launch shape for the tensor-core path. Fused needs enough (weight tile, batch tile) pairs to fill the
+// GPU; cutting the batch into shorter tiles makes more of them at the price of re-reading the weight tile
+// through L2 once per batch tile. Where even 16-row batch tiles are too few, or K is so long that one CTA
+// would stream megabytes of weights alone, the K groups are spread over CTAs instead (split).
+TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
+    TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO};
+    const int64_t G = ngroups(K);
+    const int64_t nt = (N + 127) / 128;
+    const int64_t fill = (int64_t)sm_count() * 4 / 5;
+    int bm_fill = 0;                               // tallest batch tile that still fills the GPU
+    for (int bm = 128; bm >= 16; bm >>= 1)
+        if (nt * ((M + bm - 1) / bm) >= fill) { bm_fill = bm; break; }
+    if (G <= 1) { sh.bm = bm_fill ? bm_fill : 16; return sh; }
+    const bool partials_ok = M <= SPLIT_M_MAX || G * M * N * (int64_t)sizeof(float) <= SPLIT_PARTIAL_MAX;
+    if (bm_fill && (K <= 8192 || !partials_ok)) { sh.bm = bm_fill; return sh; }
+    if (partials_ok) { sh.split = true; return sh; }
+    sh.bm = bm_fill ? bm_fill : 16;
+    return sh;
 }
 // AUTO launch shape for the CUDA-core path (reference rule: M <= 32 and more than one group).
 bool simt_auto_split(int64_t M, int64_t K) { return ngroups(K) > 1 && M <= 32; }
 
-int resolve_split(int path, bool auto_split, int64_t K, bool* split) {
-    if (path == BI_MATMUL_AUTO) *split = auto_split;
-    else if (path == BI_MATMUL_SPLIT) *split = true;
-    else if (path == BI_MATMUL_FUSED) *split = false;
-    else return fail(BI_ERR_BAD_ARG, "matmul: unknown path %d", path);
-    (void)K;
+// `path` as the ABI packs it -> kind, flags, forced batch tile, forced staging.
+struct PathArg {
+    int kind;       // BI_MATMUL_AUTO / SPLIT / FUSED / SPLIT_FOLD
+    bool zeroed;    // BI_MATMUL_WS_ZEROED
+    int bm;         // 0 = choose
+    int stage;      // TcShape::STAGE_*
+};
+int parse_path(const char* op, int path, PathArg* pa) {
+    pa->kind = path & 0xff;
+    pa->zeroed = (path & BI_MATMUL_WS_ZEROED) != 0;
+    pa->bm = (path >> 16) & 0xff;
+    pa->stage = (path & BI_QMM_STAGE_SMEM) ? TcShape::STAGE_SMEM : ((path & BI_QMM_STAGE_TMEM) ? TcShape::STAGE_TMEM : TcShape::STAGE_AUTO);
+    if (pa->kind > BI_MATMUL_SPLIT_FOLD) return fail(BI_ERR_BAD_ARG, "%s: unknown path %d", op, pa->kind);
+    if (pa->bm != 0 && pa->bm != 16 && pa->bm != 32 && pa->bm != 64 && pa->bm != 128)
+        return fail(BI_ERR_BAD_ARG, "%s: batch tile %d (16, 32, 64 or 128)", op, pa->bm);
+    if (pa->kind == BI_MATMUL_SPLIT_FOLD && !pa->zeroed)
+        return fail(BI_ERR_BAD_ARG, "%s: BI_MATMUL_SPLIT_FOLD needs BI_MATMUL_WS_ZEROED (a zeroed counter block)", op);
     return BI_OK;
 }
 
-int check_ws(const char* op, bool split, void* ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K) {
-    if (!split) return BI_OK;
-    const size_t need = (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
+// Resolve the launch shape of a tensor-core call and lay out the workspace: [counter block, if the caller says
+// it keeps one][fp32 partials].
+int tc_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K,
+             TcShape* sh, float** part) {
+    *sh = tc_auto_shape(M, N, K);
+    if (pa.kind == BI_MATMUL_SPLIT || pa.kind == BI_MATMUL_SPLIT_FOLD) { sh->split = true; sh->bm = 128; }
+    if (pa.kind == BI_MATMUL_FUSED && sh->split) {
+        sh->split = false;
+        sh->bm = 128;
+        const int64_t nt = (N + 127) / 128, fill = (int64_t)sm_count() * 4 / 5;
+        while (sh->bm > 16 && nt * ((M + sh->bm - 1) / sh->bm) < fill) sh->bm >>= 1;
+    }
+    if (pa.bm) sh->bm = pa.bm;
+    sh->stage = pa.stage;
+    const int64_t tiles = ((N + 127) / 128) * ((M + sh->bm - 1) / sh->bm);
+    const bool fold = sh->split && pa.zeroed && tiles * (int64_t)sizeof(unsigned) <= (int64_t)COUNTER_BYTES &&
+                      (pa.kind == BI_MATMUL_SPLIT_FOLD || (pa.kind == BI_MATMUL_AUTO && M <= FOLD_M_MAX));
+    if (pa.kind == BI_MATMUL_SPLIT_FOLD && !fold)
+        return fail(BI_ERR_UNSUPPORTED, "%s: %lld tiles exceed the counter block", op, (long long)tiles);
+    const size_t head = pa.zeroed ? COUNTER_BYTES : 0;
+    const size_t need = sh->split ? head + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float) : 0;
+    if (sh->split) {
+        if (!ws || ws_bytes < need) return fail(BI_ERR_WORKSPACE, "%s: split path needs %zu workspace bytes, got %zu", op, need, ws_bytes);
+        if (!aligned(ws, 16)) return fail(BI_ERR_MISALIGNED, "%s: workspace must be 16-byte aligned", op);
+    }
+    sh->counters = fold ? static_cast<unsigned*>(ws) : nullptr;
+    *part = sh->split ? reinterpret_cast<float*>(static_cast<char*>(ws) + head) : nullptr;
+    return BI_OK;
+}
+
+int simt_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K, bool* split,
+               float** part) {
+    *split = pa.kind == BI_MATMUL_AUTO ? simt_auto_split(M, K) : (pa.kind != BI_MATMUL_FUSED);
+    const size_t head = pa.zeroed ? COUNTER_BYTES : 0;
+    const size_t need = head + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
+    *part = nullptr;
+    if (!*split) return BI_OK;
     if (!ws || ws_bytes < need) return fail(BI_ERR_WORKSPACE, "%s: split path needs %zu workspace bytes, got %zu", op, need, ws_bytes);
     if (!aligned(ws, 16)) return fail(BI_ERR_MISALIGNED, "%s: workspace must be 16-byte aligned", op);
+    *part = reinterpret_cast<float*>(static_cast<char*>(ws) + head);
     return BI_OK;
 }
 
@@ -49,11 +107,11 @@ extern "C" size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int
     using namespace bi;
     (void)dtype;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    // Enough for whichever shape AUTO may pick; a forced BI_MATMUL_SPLIT always needs
-    // ceil(K/256) * M * N * 4 bytes.
+    // Enough for whichever shape AUTO may pick, with or without a counter block in front; a forced
+    // BI_MATMUL_SPLIT always needs ceil(K/256) * M * N * 4 bytes (+ BI_MATMUL_COUNTER_BYTES with BI_MATMUL_WS_ZEROED).
     if (ngroups(K) <= 1) return 0;
-    if (M > SPLIT_M_MAX && !tc_auto_split(M, N, K)) return 0;
-    return (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
+    if (M > SPLIT_M_MAX && !tc_auto_shape(M, N, K).split) return 0;
+    return COUNTER_BYTES + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
 }
 
 extern "C" size_t bi_qmm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
@@ -76,25 +134,26 @@ extern "C" int bi_matmul(const void* a, const void* b, void* out, void* workspac
     // nn.Linear's W[N, K]) that TMA can address. Decided by the weight alone.
     const bool weight_tc = dtype != BI_F32 && b_sk == 1 && K % 8 == 0 && aligned(b, 16) && (b_sn * (int64_t)es) % 16 == 0 &&
                            (N == 1 || b_sn >= K);
-    bool split;
+    PathArg pa;
+    int rc = parse_path("bi_matmul", path, &pa);
+    if (rc) return rc;
+    float* part = nullptr;
     if (weight_tc) {
         const int64_t x_ld = M == 1 ? K : a_sm;
         if (a_sk != 1 || !aligned(a, 16) || (x_ld * (int64_t)es) % 16 != 0 || x_ld < K)
             return fail(BI_ERR_MISALIGNED, "bi_matmul: activation must be k-contiguous, 16-byte aligned rows for this weight");
-        int rc = resolve_split(path, tc_auto_split(M, N, K), K, &split);
-        if (rc) return rc;
-        rc = check_ws("bi_matmul", split, workspace, workspace_bytes, M, N, K);
+        TcShape sh;
+        rc = tc_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
         if (rc) return rc;
         const int64_t w_ld = N == 1 ? K : b_sn;
-        rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, static_cast<float*>(workspace), M, N, K, dtype, split, status, st);
-        if (rc || !split) return rc;
-        return launch_combine(static_cast<float*>(workspace), out, (int)ngroups(K), M * N, dtype, st);
+        rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, part, M, N, K, dtype, sh, status, st);
+        if (rc || !sh.split || sh.counters) return rc;
+        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
     }
-    int rc = resolve_split(path, simt_auto_split(M, K), K, &split);
+    bool split;
+    rc = simt_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &split, &part);
     if (rc) return rc;
-    rc = check_ws("bi_matmul", split, workspace, workspace_bytes, M, N, K);
-    if (rc) return rc;
-    return launch_simt_matmul(a, b, out, static_cast<float*>(workspace), M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, split, st);
+    return launch_simt_matmul(a, b, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, split, st);
 }
 
 extern "C" int bi_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
@@ -116,23 +175,23 @@ extern "C" int bi_qmm(const void* x, const uint32_t* w, const void* scales, cons
 
     TcQuant q{w, scales, biases, bits, group_size};
     const bool weight_tc = dtype != BI_F32 && K % 64 == 0 && aligned(w, 16) && ((K * bits / 8) % 16) == 0;
-    bool split;
+    PathArg pa;
+    int rc = parse_path("bi_qmm", path, &pa);
+    if (rc) return rc;
+    float* part = nullptr;
     if (weight_tc) {
         const int64_t x_ld = M == 1 ? K : x_sm;
         if (!aligned(x, 16) || (x_ld * (int64_t)es) % 16 != 0)
             return fail(BI_ERR_MISALIGNED, "bi_qmm: activation must have 16-byte aligned rows for this weight");
-        int rc = resolve_split(path, tc_auto_split(M, N, K), K, &split);
+        TcShape sh;
+        rc = tc_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
         if (rc) return rc;
-        rc = check_ws("bi_qmm", split, workspace, workspace_bytes, M, N, K);
-        if (rc) return rc;
-        rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, static_cast<float*>(workspace), M, N, K, dtype, split, status, st);
-        if (rc || !split) return rc;
-        return launch_combine(static_cast<float*>(workspace), out, (int)ngroups(K), M * N, dtype, st);
+        rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, part, M, N, K, dtype, sh, status, st);
+        if (rc || !sh.split || sh.counters) return rc;
+        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
     }
-    int rc = resolve_split(path, simt_auto_split(M, K), K, &split);
+    bool split;
+    rc = simt_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &split, &part);
     if (rc) return rc;
-    rc = check_ws("bi_qmm", split, workspace, workspace_bytes, M, N, K);
-    if (rc) return rc;
-    return launch_simt_qmm(x, w, scales, biases, out, static_cast<float*>(workspace), M, N, K, M == 1 ? K : x_sm,
-                           group_size, bits, dtype, split, st);
+    return launch_simt_qmm(x, w, scales, biases, out, part, M, N, K, M == 1 ? K : x_sm, group_size, bits, dtype, split, st);
 }

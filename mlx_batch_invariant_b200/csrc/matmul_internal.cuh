@@ -27,8 +27,21 @@ struct TcQuant {
 // Returns true when the tensor-core path can take this weight / activation layout.
 bool tc_matmul_supported(const void* x, int64_t x_ld, const void* w, int64_t w_ld, int64_t N, int64_t K, int dtype,
                          const TcQuant* q);
+// Launch shape of a tensor-core matmul (every choice gives the same bits):
+//   split     one work unit per (tile, K group) writing raw fp32 partials; else one unit per tile folding in place
+//   bm        batch rows per tile: 16, 32, 64 or 128
+//   counters  split only: per-tile arrival counters (all zero) -> the last CTA of a tile folds the partials and
+//             writes `out` itself; nullptr -> the caller launches the combine kernel
+//   stage     quantized only: how the dequantized weight operand reaches the MMA
+struct TcShape {
+    enum { STAGE_AUTO = 0, STAGE_SMEM = 1, STAGE_TMEM = 2 };
+    bool split;
+    int bm;
+    unsigned* counters;
+    int stage;
+};
 int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, const TcQuant* q, void* out,
-                     float* part, int64_t M, int64_t N, int64_t K, int dtype, bool split, int32_t* status,
+                     float* part, int64_t M, int64_t N, int64_t K, int dtype, const TcShape& shape, int32_t* status,
                      cudaStream_t st);
 
 }  // namespace bi

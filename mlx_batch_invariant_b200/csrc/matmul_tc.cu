@@ -27,10 +27,21 @@
 // the other (the fused path keeps its running total in a third TMEM region).
 // For affine-quantized weights the TMA ring carries the packed codes (a deep
 // ring of small stages, so enough bytes are in flight to cover HBM latency)
-// and eight more warps turn them into the same swizzled 16-bit tile the dense
-// path would have loaded, in a short second ring (fma(float(code), scale, bias)
-// in fp32, one rounding -- mlx_batch_invariant/kernels/quantized.py:44-67), so
-// the MMA sequence is the dense one.
+// and dequantizer warps turn them into the 16-bit weight operand
+// (fma(float(code), scale, bias) in fp32, one rounding --
+// mlx_batch_invariant/kernels/quantized.py:44-67), so the MMA sequence is the
+// dense one. Two stagings of that operand exist:
+//   * tile body (batches above 64 rows): eight warps write the same swizzled
+//     shared-memory tile the dense path would have loaded;
+//   * streaming (decode, up to 64 rows): sixteen warps, one weight row per
+//     thread, write the operand straight into tensor memory (tcgen05.st) and
+//     the MMA reads its weight operand from there, so the dequantized tile
+//     never crosses shared memory and needs no proxy fence.
+//
+// The split path can fold in the producing kernel: a CTA that has stored its
+// group partial bumps a per-tile counter, and the CTA that arrives last reads
+// the G partials of the tile back in ascending g and writes T(total) -- the adds
+// and their order are those of combine_kernel, nobody waits for anybody.
 //
 // Every wait on a shared-memory barrier is bounded in time; a wait that runs
 // out records a code in the caller's status word, raises a CTA-wide abort flag
@@ -45,13 +56,16 @@ namespace bi {
 namespace {
 
 constexpr int BLOCK_N = 128;  // weight rows per tile  (UMMA M)
-constexpr int BLOCK_M = 128;  // batch rows per tile   (UMMA N)
+constexpr int BLOCK_M = 128;  // most batch rows per tile (UMMA N); a launch may use 16, 32 or 64 (Params::bm)
 constexpr int BLOCK_K = 64;   // elements per stage along K: 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BLOCK_N * BLOCK_K * 2;
-constexpr int TMEM_ACC1 = BLOCK_M;       // second accumulator
-constexpr int TMEM_TOTAL = 2 * BLOCK_M;  // running total of the fused path
 constexpr int TMEM_COLS = 512;
+// Tensor-memory columns: accumulator 0 at 0, accumulator 1 at acc_stride, the fused path's running total at
+// 2 * acc_stride (acc_stride = 128; 64 in the streaming variant, whose batch tile is at most 64 rows), and in
+// the streaming variant the weight-operand ring from column 256: 2 chunks x 4 K steps x 32 columns.
+constexpr int TMEM_A_COL0 = 256;
+constexpr int TMEM_A_STEP = BLOCK_K / 2;   // columns of one K step of the weight operand (two 16-bit values per column)
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 #ifndef BI_EPI_SLEEP_NS
 #define BI_EPI_SLEEP_NS 100
@@ -59,22 +73,27 @@ constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 constexpr int MAX_SLOTS = 8;     // ring depths and the chunk-completion barrier array (power of two)
 constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EPI0 = 2, WARP_DEQ0 = 6;
-constexpr int N_DEQ_WARPS = 8;
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int BAR_BYTES = 512;
 
-template <int QBITS> struct Cfg {
+// TSA: the weight ("A") operand of the MMA comes from tensor memory (streaming quantized variant).
+template <int QBITS, bool TSA> struct Cfg {
     static constexpr int RAW_BYTES = QBITS ? BLOCK_N * BLOCK_K * QBITS / 8 : 0;
-    static constexpr int THREADS = QBITS ? 32 * (WARP_DEQ0 + N_DEQ_WARPS) : 192;
+    static constexpr int N_DEQ_WARPS = QBITS ? (TSA ? 16 : 8) : 0;
+    static constexpr int THREADS = 32 * (WARP_DEQ0 + N_DEQ_WARPS);
 };
+constexpr int TSA_SMEM_CAP = 164 * 1024;   // leaves the L1 its share: the streaming dequantizers read scales through it
 
 // Shared memory, in this order (every tile 1024-byte aligned):
 //   x ring     load_slots x ks x x_bytes  activation tiles (TMA, 128-byte swizzle). Only the batch rows
 //                                         that exist are loaded; the MMA still reads 128 rows from the
 //                                         tile base, so the ring sits first and what follows it is
 //                                         valid (unread-result) memory.
-//   W ring     dense: load_slots x ks x 16 KB (TMA)   quantized: w_slots x ks x 16 KB (dequantizers)
-//   raw ring   quantized only: load_slots x ks x RAW_BYTES packed codes (TMA, no swizzle)
+//   W ring     dense: load_slots x ks x 16 KB (TMA)   quantized tile body: w_slots x ks x 16 KB (dequantizers)
+//              streaming: none (the operand lives in tensor memory)
+//   raw ring   quantized only: load_slots x ks x RAW_BYTES packed codes (TMA; no swizzle for the tile
+//              body, 32- or 64-byte swizzle for the streaming variant so that a thread per row reads
+//              its 16-byte pieces without bank conflicts)
 //   barriers
 struct Params {
     void* out;          // [M, N] in T (fused)
@@ -82,8 +101,10 @@ struct Params {
     const void* scales; // quantized only: [N, K/gs] in T
     const void* biases;
     int32_t* status;
+    unsigned* counters; // split path with in-kernel fold: one arrival counter per (weight tile, batch tile), zero between calls
     int M, N, K, G;
     int n_tiles, m_tiles;
+    int bm;             // batch rows per tile: 16, 32, 64 or 128 (launch shape; an output column's bits do not depend on it)
     int split;          // 1: split jobs, 0: fused units
     int x_rows;         // rows of the activation TMA box
     int box3d;          // 1: one TMA box holds a whole chunk (all K steps of a slot) of an operand
@@ -93,6 +114,7 @@ struct Params {
     int load_slots;     // depth of the TMA ring, in chunks
     int w_slots;        // depth of the dequantized-weight ring (quantized), in chunks
     int w_ring_slots;   // slots of the ring the MMA reads weights from (w_slots, or load_slots when dense)
+    int acc_stride;     // tensor-memory columns between the two accumulators
     int gs;
     long long units;
 };
@@ -102,32 +124,16 @@ enum { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_EPI = 3, ROLE_DEQ = 4 };
 struct Ctl {
     int32_t* status;
     volatile int* abort_flag;  // shared memory
-#ifdef BI_TC_PROFILE
-    long long* waited;         // cycles this thread spent in wait_bounded
-#endif
 };
 
 __device__ __forceinline__ void report(const Ctl& c, int role, int idx) {
     *c.abort_flag = 1;
-#ifndef BI_TC_PROFILE
     if (c.status) atomicCAS(c.status, 0, (int)(0x10000 | (role << 8) | (idx & 0xff)));
-#endif
 }
 
 // Wait for barrier phase `parity` to complete. Gives up after WAIT_LIMIT_NS or when another
 // role has raised the abort flag; returns false then.
-__device__ __forceinline__ bool wait_bounded_impl(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx);
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx) {
-#ifdef BI_TC_PROFILE
-    const long long t0 = clock64();
-    const bool ok = wait_bounded_impl(bar, parity, c, role, idx);
-    *c.waited += clock64() - t0;
-    return ok;
-#else
-    return wait_bounded_impl(bar, parity, c, role, idx);
-#endif
-}
-__device__ __forceinline__ bool wait_bounded_impl(uint32_t bar, uint32_t parity, const Ctl& c, int role, int idx) {
     if (role == ROLE_EPI || role == ROLE_DEQ) {
         // whole warps wait here; back off so they do not take issue slots from the TMA and MMA threads
         for (int i = 0; i < 2048; ++i) {
@@ -233,7 +239,7 @@ struct ChunkIter {
     }
     __device__ __forceinline__ bool valid() const { return left > 0; }
     __device__ __forceinline__ int n0() const { return nt * BLOCK_N; }
-    __device__ __forceinline__ int m0() const { return mt * BLOCK_M; }
+    __device__ __forceinline__ int m0() const { return mt * p.bm; }
     __device__ __forceinline__ int ksteps() const { return min(p.ks, nst - c * p.ks); }
     __device__ __forceinline__ int k0() const { return g * GROUP_K + c * p.ks * BLOCK_K; }
     __device__ __forceinline__ bool first_in_group() const { return c == 0; }
@@ -257,18 +263,61 @@ struct ChunkIter {
     }
 };
 
+// One weight row's 64 codes of a K step -> 32 packed pairs of T, written to the row's tensor-memory lane at
+// columns taddr .. taddr+31 (column c holds elements 2c and 2c+1 of the row, low half first) in two stores of
+// 16 columns. `raw` is the K step's tile of packed codes as the swizzled TMA box left it; (s2a, b2a) apply to
+// codes 0..31, (s2b, b2b) to codes 32..63.
 template <typename T, int QBITS>
-__global__ void __launch_bounds__(Cfg<QBITS>::THREADS, 1)
+__device__ __forceinline__ void dequant_row64_to_tmem(const uint8_t* raw, int row, uint64_t s2a, uint64_t b2a, uint64_t s2b,
+                                                      uint64_t b2b, uint32_t taddr) {
+    constexpr int ROW_BYTES = BLOCK_K * QBITS / 8;       // 32 (4-bit) or 64 (8-bit)
+    constexpr int PIECES = ROW_BYTES / 16;               // 16-byte pieces per row
+    constexpr int HP = PIECES / 2;                       // pieces behind 32 codes
+    // TMA swizzle: the 16-byte piece index is XORed with address bits [7, 7 + log2(PIECES))
+    const int sw = QBITS == 4 ? ((row >> 2) & 1) : ((row >> 1) & 3);
+    const uint8_t* rp = raw + row * ROW_BYTES;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint64_t s2 = h ? s2b : s2a, b2 = h ? b2b : b2a;
+        uint32_t o[16];
+#pragma unroll
+        for (int cc = 0; cc < HP; ++cc) {
+            const int c = h * HP + cc;
+            const uint4 q = *reinterpret_cast<const uint4*>(rp + ((c ^ sw) << 4));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            if (QBITS == 4) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 v = dequant8<T, 4>(&w[i], s2, b2);
+                    o[i * 4 + 0] = v.x; o[i * 4 + 1] = v.y; o[i * 4 + 2] = v.z; o[i * 4 + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint4 v = dequant8<T, 8>(&w[2 * i], s2, b2);
+                    o[(cc * 2 + i) * 4 + 0] = v.x; o[(cc * 2 + i) * 4 + 1] = v.y;
+                    o[(cc * 2 + i) * 4 + 2] = v.z; o[(cc * 2 + i) * 4 + 3] = v.w;
+                }
+            }
+        }
+        ptx::tmem_st_32x16(taddr + 16u * h, o);
+    }
+}
+
+template <typename T, int QBITS, bool TSA>
+__global__ void __launch_bounds__((Cfg<QBITS, TSA>::THREADS), 1)
 tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const Params p) {
-    using C = Cfg<QBITS>;
+    using C = Cfg<QBITS, TSA>;
+    static_assert(!TSA || QBITS != 0, "the tensor-memory weight operand exists for quantized weights only");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     const int LS = p.load_slots, KS = p.ks;
-    const int WS = QBITS ? p.w_slots : p.load_slots;
+    const int WS = QBITS ? p.w_slots : p.load_slots;                 // slots of the weight-operand ring
+    const int WS_SMEM = TSA ? 0 : WS;                                // ... of which live in shared memory
     const uint32_t w_ring = smem_base + (uint32_t)(LS * KS) * p.x_bytes;
-    const uint32_t raw_ring = w_ring + (uint32_t)(WS * KS) * W_TILE_BYTES;
+    const uint32_t raw_ring = w_ring + (uint32_t)(WS_SMEM * KS) * W_TILE_BYTES;
     const uint32_t bar_base = raw_ring + (uint32_t)(LS * KS) * C::RAW_BYTES;
     auto x_tile = [&](int l, int j) { return smem_base + (uint32_t)(l * KS + j) * p.x_bytes; };
     auto w_tile = [&](int w, int j) { return w_ring + (uint32_t)(w * KS + j) * W_TILE_BYTES; };
@@ -277,29 +326,26 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     auto bar_wfull = [&](int w) { return bar_base + 8u * (MAX_SLOTS + w); };      // dequantized chunk ready
     auto bar_done = [&](int d) { return bar_base + 8u * (2 * MAX_SLOTS + d); };   // MMAs of a chunk complete
     auto bar_tempty = [&](int b) { return bar_base + 8u * (3 * MAX_SLOTS + b); }; // accumulator drained
-    uint8_t* misc = smem_gen + (bar_base - smem_base) + 8 * (3 * MAX_SLOTS + 2);
+    const uint32_t bar_epi = bar_base + 8u * (3 * MAX_SLOTS + 2);                 // the four epilogue warps meet here
+    uint8_t* misc = smem_gen + (bar_base - smem_base) + 8 * (3 * MAX_SLOTS + 3);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 4);
+    volatile int* fold_flag = reinterpret_cast<volatile int*>(misc + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef BI_TC_PROFILE
-    long long waited = 0;
-    const long long t_start = clock64();
-    const uint64_t t_start_ns = ptx::globaltimer_ns();
-    const Ctl ctl{p.status, abort_flag, &waited};
-#else
     const Ctl ctl{p.status, abort_flag};
-#endif
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *fold_flag = 0;
         for (int i = 0; i < MAX_SLOTS; ++i) {
             ptx::mbar_init(bar_lfull(i), 1);
-            ptx::mbar_init(bar_wfull(i), N_DEQ_WARPS);
+            ptx::mbar_init(bar_wfull(i), C::N_DEQ_WARPS ? C::N_DEQ_WARPS : 1);
             ptx::mbar_init(bar_done(i), 1);
         }
         for (int b = 0; b < 2; ++b) ptx::mbar_init(bar_tempty(b), 4);
+        ptx::mbar_init(bar_epi, 4);
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_w);
         ptx::prefetch_tensormap(&tmap_x);
@@ -312,6 +358,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_total = 2u * (uint32_t)p.acc_stride;
 
     const int ub = (int)(p.units * blockIdx.x / gridDim.x);
     const int ue = (int)(p.units * (blockIdx.x + 1) / gridDim.x);
@@ -330,7 +377,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             // box that lie beyond K are zero-filled and still count towards the barrier's bytes.
             const uint32_t xb = (uint32_t)p.x_rows * BLOCK_K * 2;
             const uint32_t wb = QBITS ? (uint32_t)C::RAW_BYTES : (uint32_t)W_TILE_BYTES;
-            const bool w3d = p.box3d && !QBITS;
+            const bool w3d = p.box3d && (!QBITS || TSA);
             // Weight tiles go through L2 marked evict-first: they should not push the batch rows or the split
             // path's partials out (measured faster also where several batch tiles re-read a weight tile).
             const uint64_t w_policy = ptx::l2_policy_evict_first();
@@ -343,13 +390,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t bar = bar_lfull(l);
                 ptx::mbar_expect_tx(bar, xb * (uint32_t)(p.box3d ? KS : kc) + wb * (uint32_t)(w3d ? KS : kc));
                 const int n0 = it.n0(), m0 = it.m0();
-                if (w3d) ptx::tma_load_3d_hint(w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar, w_policy);
+                if (w3d) ptx::tma_load_3d_hint(QBITS ? raw_tile(l, 0) : w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar, w_policy);
                 if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, it.k0() >> 6, bar);
                 if (!w3d || !p.box3d) {
                     for (int j = 0; j < kc; ++j) {
                         const int k0 = it.k0() + j * BLOCK_K;
-                        if (QBITS) ptx::tma_load_2d_hint(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar, w_policy);
-                        else if (!w3d) ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
+                        if (!w3d) {
+                            if (QBITS) ptx::tma_load_2d_hint(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar, w_policy);
+                            else ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
+                        }
                         if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
                     }
                 }
@@ -369,68 +418,62 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             // The MMA's N is the batch rows that were loaded, rounded up to the 16 the instruction wants
-            // (columns past the loaded rows see whatever follows in the ring and are never read back).
+            // (columns past the loaded rows see whatever follows in the ring and are never read back; an
+            // accumulator column depends on its own batch row only, whatever N is).
             const uint32_t mma_n = (uint32_t)((p.x_rows + 15) & ~15);
             const uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((mma_n >> 3) << 17) |
                                    ((uint32_t)(BLOCK_N >> 4) << 24);
             int job = -1; bool ok = true;
             uint32_t tmem_d = tmem_base;
-#ifdef BI_TC_PROFILE
-            long long prof_fence = 0, prof_mma = 0, prof_commit = 0;
-#endif
             for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
                 if (it.first_in_group()) {
                     ++job;
                     const int buf = job & 1;
                     if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
-                    tmem_d = tmem_base + (uint32_t)buf * TMEM_ACC1;
+                    tmem_d = tmem_base + (uint32_t)(buf * p.acc_stride);
                 }
                 const int l = it.l, w = it.w;
                 const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
                 if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
-#ifdef BI_TC_PROFILE
-                const long long tq0 = clock64();
-#endif
                 ptx::tc_fence_after();
-#ifdef BI_TC_PROFILE
-                const long long tq1 = clock64();
-#endif
                 const int kc = it.ksteps();
                 const int kend = min(p.K, (it.g + 1) * GROUP_K);
                 for (int j = 0; j < kc; ++j) {
                     const int kleft = kend - (it.k0() + j * BLOCK_K);
                     // one descriptor per operand and K step of 64; a UMMA K step of 16 elements is
                     // +32 bytes, i.e. +2 in the descriptor's 16-byte address field
-                    const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
                     const uint64_t db = ptx::smem_desc_sw128(x_tile(l, j));
-                    if (kleft >= BLOCK_K) {
-                        if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
-                        else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
-                        ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
+                    if constexpr (TSA) {
+                        // weight operand in tensor memory: a UMMA K step of 16 elements is 8 columns
+                        const uint32_t ta = tmem_base + (uint32_t)(TMEM_A_COL0 + (w * KS + j) * TMEM_A_STEP);
+                        if (kleft >= BLOCK_K) {
+                            if (it.c | j) ptx::umma_f16_ts_c<true>(tmem_d, ta, db, IDESC);
+                            else          ptx::umma_f16_ts_c<false>(tmem_d, ta, db, IDESC);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 8, db + 2, IDESC);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 16, db + 4, IDESC);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 24, db + 6, IDESC);
+                        } else {
+                            const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
+                            for (int kk = 0; kk < nsteps; ++kk)
+                                ptx::umma_f16_ts(tmem_d, ta + 8 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        }
                     } else {
-                        const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
-                        for (int kk = 0; kk < nsteps; ++kk)
-                            ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
+                        if (kleft >= BLOCK_K) {
+                            if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
+                            else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
+                        } else {
+                            const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
+                            for (int kk = 0; kk < nsteps; ++kk)
+                                ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        }
                     }
                 }
-#ifdef BI_TC_PROFILE
-                const long long tq2 = clock64();
-#endif
                 ptx::umma_commit(bar_done(it.d));
-#ifdef BI_TC_PROFILE
-                const long long tq3 = clock64();
-                prof_fence += tq1 - tq0; prof_mma += tq2 - tq1; prof_commit += tq3 - tq2;
-#endif
             }
-#ifdef BI_TC_PROFILE
-            if (p.status) {
-                unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
-                atomicAdd(c + 8, (unsigned long long)prof_fence); atomicAdd(c + 9, (unsigned long long)prof_mma);
-                atomicAdd(c + 10, (unsigned long long)prof_commit);
-            }
-#endif
         }
     } else if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4) {
         // ------------------------------------------------------------ epilogue
@@ -438,6 +481,15 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int row = quad * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
         int job = -1; bool ok = true;
+        uint32_t epi_ph = 0;
+        // the four epilogue warps meet (bounded, like every other wait of the kernel)
+        auto epi_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_epi);
+            const bool r = wait_bounded(bar_epi, epi_ph, ctl, ROLE_EPI, 40);
+            epi_ph ^= 1u;
+            return r;
+        };
         T* out = static_cast<T*>(p.out);
         for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
             if (it.first_in_group()) ++job;
@@ -448,20 +500,21 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int g = it.g;
             const int n = it.n0() + row;
             const int m0 = it.m0();
-            const int ncols = min(BLOCK_M, p.M - m0);
-            const uint32_t acc = lane_base + (uint32_t)buf * TMEM_ACC1;
+            const int ncols = min(p.bm, p.M - m0);
+            const uint32_t acc = lane_base + (uint32_t)(buf * p.acc_stride);
             const bool first = g == 0, last = g == p.G - 1;
             if (p.split) {
                 // A TMEM load queues behind the MMAs already issued for the next unit, so the loads of two
-                // column blocks go out together and pay that wait once.
+                // column blocks go out together and pay that wait once (the streaming variant, short of
+                // registers with its sixteen dequantizer warps, takes one block at a time).
 #pragma unroll 1
-                for (int c = 0; c * 32 < ncols; c += 2) {  // warp-uniform trip count
-                    uint32_t v0[32], v1[32];
-                    const bool two = (c + 1) * 32 < ncols;
+                for (int c = 0; c * 32 < ncols; c += (TSA ? 1 : 2)) {  // warp-uniform trip count
+                    uint32_t v0[32], v1[TSA ? 1 : 32];
+                    const bool two = !TSA && (c + 1) * 32 < ncols;
                     ptx::tmem_ld_32x32(acc + c * 32, v0);
-                    if (two) ptx::tmem_ld_32x32(acc + c * 32 + 32, v1);
+                    if constexpr (!TSA) { if (two) ptx::tmem_ld_32x32(acc + c * 32 + 32, v1); }
                     ptx::tmem_ld_wait();
-                    if ((c + 2) * 32 >= ncols) {
+                    if ((c + (TSA ? 1 : 2)) * 32 >= ncols) {
                         // the accumulator is in registers: hand it back before the stores go out
                         ptx::tc_fence_before();
                         __syncwarp();
@@ -469,41 +522,86 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                     if (n < p.N) {
                         float* dst = p.part + ((long long)g * p.M + m0 + c * 32) * p.N + n;
-                        const int left = p.M - (m0 + c * 32);
+                        const int left = ncols - c * 32;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (j < left) dst[(long long)j * p.N] = __uint_as_float(v0[j]);
-                        if (two) {
+                        if constexpr (!TSA) {
+                            if (two) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (32 + j < left) dst[(long long)(32 + j) * p.N] = __uint_as_float(v1[j]);
+                                for (int j = 0; j < 32; ++j)
+                                    if (32 + j < left) dst[(long long)(32 + j) * p.N] = __uint_as_float(v1[j]);
+                            }
+                        }
+                    }
+                }
+                if (p.counters) {
+                    // In-kernel fold. Every thread's partial stores are fenced device-wide, the four warps meet,
+                    // one thread counts this unit in; the CTA that counts in last (all G partials of the tile are
+                    // then visible) folds them in ascending g and writes the output. The counter goes back to 0.
+                    __threadfence();
+                    if (!epi_sync()) { ok = false; break; }
+                    if (warp == WARP_EPI0 && lane == 0) {
+                        unsigned* ctr = p.counters + ((long long)it.nt * p.m_tiles + it.mt);
+                        const unsigned old = atomicAdd(ctr, 1u);
+                        const int mine = old == (unsigned)p.G - 1u;
+                        if (mine) atomicExch(ctr, 0u);
+                        *fold_flag = mine;
+                    }
+                    if (!epi_sync()) { ok = false; break; }
+                    if (*fold_flag) {
+                        __threadfence();
+                        if (n < p.N) {
+                            const long long gstride = (long long)p.M * p.N;
+#pragma unroll 1
+                            for (int mm = 0; mm < ncols; mm += 4) {
+                                const float* src = p.part + (long long)(m0 + mm) * p.N + n;
+                                float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+                                for (int gg = 0; gg < p.G; ++gg) {
+                                    float v[4];
+#pragma unroll
+                                    for (int u = 0; u < 4; ++u)
+                                        v[u] = (mm + u < ncols) ? __ldcg(src + gg * gstride + (long long)u * p.N) : 0.0f;
+#pragma unroll
+                                    for (int u = 0; u < 4; ++u) tot[u] = add_rn(tot[u], v[u]);
+                                }
+#pragma unroll
+                                for (int u = 0; u < 4; ++u)
+                                    if (mm + u < ncols) out[(long long)(m0 + mm + u) * p.N + n] = Cvt<T>::down(tot[u]);
+                            }
                         }
                     }
                 }
             }
+            // fused: the running total lives in TMEM; total = total + p_g, from an exact 0. EW columns at a time
+            // (16 in the streaming variant, which is short of registers).
+            constexpr int EW = TSA ? 16 : 32;
 #pragma unroll 1
-            for (int c = 0; !p.split && c * 32 < ncols; ++c) {  // warp-uniform trip count
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(acc + c * 32, v);
-                {
-                    // fused: the running total lives in TMEM; total = total + p_g, from an exact 0
-                    uint32_t t[32];
-                    if (!first) ptx::tmem_ld_32x32(lane_base + TMEM_TOTAL + c * 32, t);
-                    ptx::tmem_ld_wait();
+            for (int c = 0; !p.split && c * EW < ncols; ++c) {  // warp-uniform trip count
+                uint32_t v[EW], t[EW];
+                if constexpr (TSA) {
+                    ptx::tmem_ld_32x16(acc + c * EW, v);
+                    if (!first) ptx::tmem_ld_32x16(lane_base + tmem_total + c * EW, t);
+                } else {
+                    ptx::tmem_ld_32x32(acc + c * EW, v);
+                    if (!first) ptx::tmem_ld_32x32(lane_base + tmem_total + c * EW, t);
+                }
+                ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        t[j] = __float_as_uint(add_rn(first ? 0.0f : __uint_as_float(t[j]), __uint_as_float(v[j])));
-                    if (last) {
-                        if (n < p.N) {
+                for (int j = 0; j < EW; ++j)
+                    t[j] = __float_as_uint(add_rn(first ? 0.0f : __uint_as_float(t[j]), __uint_as_float(v[j])));
+                if (last) {
+                    if (n < p.N) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int m = m0 + c * 32 + j;
-                                if (m < p.M) out[(long long)m * p.N + n] = Cvt<T>::down(__uint_as_float(t[j]));
-                            }
+                        for (int j = 0; j < EW; ++j) {
+                            const int m = m0 + c * EW + j;
+                            if (c * EW + j < ncols) out[(long long)m * p.N + n] = Cvt<T>::down(__uint_as_float(t[j]));
                         }
-                    } else {
-                        ptx::tmem_st_32x32(lane_base + TMEM_TOTAL + c * 32, t);
                     }
+                } else {
+                    if constexpr (TSA) ptx::tmem_st_32x16(lane_base + tmem_total + c * EW, t);
+                    else ptx::tmem_st_32x32(lane_base + tmem_total + c * EW, t);
                 }
             }
             if (!p.split) {
@@ -513,8 +611,8 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));
             }
         }
-    } else if (QBITS && warp >= WARP_DEQ0) {
-        // ------------------------------------------------------------ dequantizers
+    } else if (QBITS && !TSA && warp >= WARP_DEQ0) {
+        // ------------------------------------------------------------ dequantizers (tile body)
         // 256 threads: thread t turns half a weight row (32 codes) of every K step into four
         // 16-byte chunks of the swizzled tile. Two threads per row, so a warp reads 512 contiguous
         // bytes of packed codes and its stores spread over all banks.
@@ -613,20 +711,73 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_wfull(w));
         }
-    }
-
-#ifdef BI_TC_PROFILE
-    // development build: status is an array of 16 int64 counters (per role: waited, busy)
-    if (p.status && lane == 0) {
-        const int role = warp == WARP_TMA ? 0 : warp == WARP_MMA ? 1 : warp == WARP_EPI0 ? 2 : warp == WARP_DEQ0 ? 3 : -1;
-        if (role >= 0) {
-            unsigned long long* c = reinterpret_cast<unsigned long long*>(p.status);
-            atomicAdd(c + 2 * role, (unsigned long long)waited);
-            atomicAdd(c + 2 * role + 1, (unsigned long long)(clock64() - t_start));
-            if (role == 2) { atomicMax(c + 11, (unsigned long long)(clock64() - t_start)); atomicMax(c + 12, (unsigned long long)(ptx::globaltimer_ns() - t_start_ns)); }
+    } else if (QBITS && TSA && warp >= WARP_DEQ0) {
+        // ------------------------------------------------------------ dequantizers (streaming)
+        // Sixteen warps. A warp may touch the 32 tensor-memory lanes of its quadrant (warp index mod 4)
+        // only, so the four warps of a quadrant share its 32 weight rows by K step: warp (quadrant, j)
+        // dequantizes K step j of every chunk -- one row, 64 codes, per thread -- and writes the 32
+        // packed columns with one tcgen05.st. Scales and biases are read straight from global memory,
+        // DEPTH chunks ahead of their use (a register queue), through the L1.
+        constexpr int QB = QBITS ? QBITS : 4;
+        constexpr int DEPTH = 4;
+        const int dw = warp - WARP_DEQ0;
+        const int quad = warp & 3;
+        const int jstep = dw >> 2;                                           // 0..3
+        const int row = quad * 32 + lane;
+        const unsigned short* scales = static_cast<const unsigned short*>(p.scales);
+        const unsigned short* biases = static_cast<const unsigned short*>(p.biases);
+        const int groups_per_row = p.K / p.gs;
+        const int gs_shift = p.gs == 32 ? 5 : (p.gs == 64 ? 6 : 7);
+        const bool two_entries = p.gs == 32;                                 // a K step of 64 spans two quantization groups
+        // entries of (row n, K step starting at k): low half = first entry, high half = second (gs 32) or the same
+        auto fetch = [&](const ChunkIter& c, uint32_t& sv, uint32_t& bv) {
+            sv = 0u; bv = 0u;
+            if (!c.valid()) return;
+            const int n = c.n0() + row;
+            if (n >= p.N || jstep >= c.ksteps()) return;
+            const long long e = (long long)n * groups_per_row + ((c.k0() + jstep * BLOCK_K) >> gs_shift);
+            if (two_entries) {
+                sv = __ldg(reinterpret_cast<const unsigned int*>(scales + e));
+                bv = __ldg(reinterpret_cast<const unsigned int*>(biases + e));
+            } else {
+                sv = __ldg(scales + e); sv |= sv << 16;
+                bv = __ldg(biases + e); bv |= bv << 16;
+            }
+        };
+        auto to_f = [&](uint32_t h) {
+            T tv;
+            *reinterpret_cast<unsigned short*>(&tv) = (unsigned short)h;
+            return Cvt<T>::up(tv);
+        };
+        uint32_t qs[DEPTH], qb[DEPTH];
+        ChunkIter pf(p, ub, ue);
+#pragma unroll
+        for (int i = 0; i < DEPTH; ++i) { fetch(pf, qs[i], qb[i]); if (pf.valid()) pf.next(); }
+        const uint32_t a_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)TMEM_A_COL0;
+        bool ok = true;
+        for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
+            const uint32_t sv = qs[0], bv = qb[0];
+#pragma unroll
+            for (int i = 0; i + 1 < DEPTH; ++i) { qs[i] = qs[i + 1]; qb[i] = qb[i + 1]; }
+            fetch(pf, qs[DEPTH - 1], qb[DEPTH - 1]);
+            if (pf.valid()) pf.next();
+            const int l = it.l, w = it.w;
+            if (!wait_bounded(bar_lfull(l), it.lph, ctl, ROLE_DEQ, l)) { ok = false; break; }
+            if (it.ci >= WS && !wait_done(it.ci - WS, ROLE_DEQ)) { ok = false; break; }
+            if (jstep < it.ksteps()) {
+                ptx::tc_fence_after();
+                const float s0 = to_f(sv & 0xffffu), s1 = to_f(sv >> 16), b0 = to_f(bv & 0xffffu), b1 = to_f(bv >> 16);
+                dequant_row64_to_tmem<T, QB>(smem_gen + (raw_tile(l, jstep) - smem_base), row, ptx::pack2(s0, s0), ptx::pack2(b0, b0),
+                                             ptx::pack2(s1, s1), ptx::pack2(b1, b1),
+                                             a_lane + (uint32_t)((w * KS + jstep) * TMEM_A_STEP));
+                ptx::tmem_st_wait();
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_wfull(w));
         }
     }
-#endif
+
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == WARP_MMA) {
@@ -634,6 +785,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
+
 
 // ---- host side -----------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -667,42 +819,36 @@ int make_map(CUtensorMap* m, CUtensorMapDataType dt, size_t esize, const void* b
     return BI_OK;
 }
 
-// The same tensor seen as [K/64 blocks][rows][64 elements] (needs K % 64 == 0): a box of `depth` blocks lands
-// as `depth` consecutive K-step tiles of box_rows x 128 bytes.
+// The same tensor seen as [K/64 blocks][rows][inner elements] (needs K % 64 == 0; inner = the elements that hold
+// 64 values of K: 64 for 16-bit data, 8 or 16 words for packed codes): a box of `depth` blocks lands as `depth`
+// consecutive K-step tiles of box_rows x (inner * esize) bytes.
 int make_map3(CUtensorMap* m, CUtensorMapDataType dt, size_t esize, const void* base, uint64_t kblocks, uint64_t rows,
-              uint64_t ld, uint32_t box_rows, uint32_t depth) {
+              uint64_t ld, uint32_t box_rows, uint32_t depth, uint32_t inner = BLOCK_K,
+              CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(BI_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t gdim[3] = {(cuuint64_t)BLOCK_K, rows, kblocks};
-    cuuint64_t gstr[2] = {ld * esize, (cuuint64_t)BLOCK_K * esize};
-    cuuint32_t box[3] = {(cuuint32_t)BLOCK_K, box_rows, depth};
+    cuuint64_t gdim[3] = {(cuuint64_t)inner, rows, kblocks};
+    cuuint64_t gstr[2] = {ld * esize, (cuuint64_t)inner * esize};
+    cuuint32_t box[3] = {(cuuint32_t)inner, box_rows, depth};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(m, dt, 3, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(BI_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
     return BI_OK;
-}
-
-int sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-    return cached[dev] > 0 ? cached[dev] : 148;
 }
 
 // Chunk size and ring depths from the shared-memory budget (a launch-shape choice; no arithmetic
 // depends on it): the largest chunk that still leaves at least two slots in every ring. Measured: larger
 // chunks beat deeper rings (each chunk costs the MMA thread one commit and one pass of its loop).
 // raw_bytes: packed codes per K step of a quantized weight tile, 0 for dense weights.
-bool pick_rings(Params& p, int raw_bytes) {
+// tsa: streaming quantized variant (weight operand in tensor memory: its ring of two chunks takes no shared memory).
+bool pick_rings(Params& p, int raw_bytes, bool tsa) {
     const bool quant = raw_bytes != 0;
-    const int avail = SMEM_LIMIT - 1024 - BAR_BYTES;
+    const int avail = (tsa ? TSA_SMEM_CAP : SMEM_LIMIT) - 1024 - BAR_BYTES;
     p.w_slots = quant ? 2 : 0;
     p.ks = 0;
-    for (int ks = 4; ks >= 1; ks >>= 1) {
-        const int wring = p.w_slots * ks * W_TILE_BYTES;
+    for (int ks = 4; ks >= (tsa ? 4 : 1); ks >>= 1) {
+        const int wring = (tsa ? 0 : p.w_slots) * ks * W_TILE_BYTES;
         const int slot = ks * (p.x_bytes + (quant ? raw_bytes : W_TILE_BYTES));
         const int ls = (avail - wring) / slot;
         if (ls >= 2) { p.ks = ks; p.load_slots = ls < MAX_SLOTS ? ls : MAX_SLOTS; break; }
@@ -710,14 +856,14 @@ bool pick_rings(Params& p, int raw_bytes) {
     if (!p.ks) return false;
     p.w_ring_slots = quant ? p.w_slots : p.load_slots;
     p.smem_bytes = 1024 + BAR_BYTES + p.load_slots * p.ks * (p.x_bytes + raw_bytes) +
-                   (quant ? p.w_slots : p.load_slots) * p.ks * W_TILE_BYTES;
+                   (quant ? (tsa ? 0 : p.w_slots) : p.load_slots) * p.ks * W_TILE_BYTES;
     return true;
 }
 
-template <typename T, int QBITS>
+template <typename T, int QBITS, bool TSA>
 int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cudaStream_t st) {
-    using C = Cfg<QBITS>;
-    auto kern = tc_matmul_kernel<T, QBITS>;
+    using C = Cfg<QBITS, TSA>;
+    auto kern = tc_matmul_kernel<T, QBITS, TSA>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -756,28 +902,43 @@ bool tc_matmul_supported(const void* x, int64_t x_ld, const void* w, int64_t w_l
 }
 
 int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, const TcQuant* q, void* out,
-                     float* part, int64_t M, int64_t N, int64_t K, int dtype, bool split, int32_t* status,
+                     float* part, int64_t M, int64_t N, int64_t K, int dtype, const TcShape& shape, int32_t* status,
                      cudaStream_t st) {
     const bool quant = q && q->codes;
+    const bool split = shape.split;
+    const int bm = shape.bm;
+    if (bm != 16 && bm != 32 && bm != 64 && bm != BLOCK_M) return fail(BI_ERR_BAD_ARG, "matmul: batch tile %d (16, 32, 64 or 128)", bm);
     Params p{};
     p.out = out; p.part = part; p.status = status;
+    p.counters = split ? shape.counters : nullptr;
     p.scales = quant ? q->scales : nullptr; p.biases = quant ? q->biases : nullptr;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.G = (int)((K + GROUP_K - 1) / GROUP_K);
+    p.bm = bm;
     p.n_tiles = (int)((N + BLOCK_N - 1) / BLOCK_N);
-    p.m_tiles = (int)((M + BLOCK_M - 1) / BLOCK_M);
+    p.m_tiles = (int)((M + bm - 1) / bm);
     p.split = split ? 1 : 0;
     p.gs = quant ? q->gs : 0;
     p.units = (long long)p.n_tiles * p.m_tiles * (split ? p.G : 1);
     if (p.units >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "matmul: %lld work units exceed the kernel's 32-bit unit index", p.units);
     // Only the batch rows that exist are loaded; the box height is a launch-shape choice.
-    const int64_t mr = M < BLOCK_M ? ((M + 7) / 8) * 8 : BLOCK_M;
+    const int64_t mr = M < bm ? ((M + 7) / 8) * 8 : bm;
     p.x_rows = (int)mr;
     p.x_bytes = ((int)mr * BLOCK_K * 2 + 1023) / 1024 * 1024;
-
-    if (!pick_rings(p, quant ? BLOCK_N * BLOCK_K * q->bits / 8 : 0))
-        return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
     p.box3d = K % BLOCK_K == 0 ? 1 : 0;
+    // Quantized weights: the streaming staging (weight operand in tensor memory) serves batch tiles of up to
+    // 64 rows, the tile body the rest. Same MMA sequence on the same operand values either way.
+    bool tsa = quant && mr <= 64 && p.box3d && shape.stage != TcShape::STAGE_SMEM;
+    if (quant && shape.stage == TcShape::STAGE_TMEM && !tsa)
+        return fail(BI_ERR_UNSUPPORTED, "qmm: the tensor-memory staging needs a batch tile of at most 64 rows");
+    p.acc_stride = tsa ? 64 : BLOCK_M;
+
+    if (!pick_rings(p, quant ? BLOCK_N * BLOCK_K * q->bits / 8 : 0, tsa)) {
+        if (!tsa || shape.stage == TcShape::STAGE_TMEM || !pick_rings(p, BLOCK_N * BLOCK_K * q->bits / 8, false))
+            return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
+        tsa = false;
+        p.acc_stride = BLOCK_M;
+    }
 
     const CUtensorMapDataType dt = dtype == BI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mw, mx;
@@ -786,6 +947,7 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
         // A driver that refuses the 3-D view gets the per-K-step boxes instead; the bytes that land are the same.
         rc = make_map3(&mx, dt, 2, x, (uint64_t)(K / BLOCK_K), (uint64_t)M, (uint64_t)x_ld, (uint32_t)p.x_rows, (uint32_t)p.ks);
         if (!rc && !quant) rc = make_map3(&mw, dt, 2, w, (uint64_t)(K / BLOCK_K), (uint64_t)N, (uint64_t)w_ld, BLOCK_N, (uint32_t)p.ks);
+        if (rc && tsa) return rc;
         if (rc) p.box3d = 0;
     }
     if (!p.box3d) {
@@ -796,17 +958,25 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     }
     if (quant) {
         const uint64_t words = (uint64_t)K * q->bits / 32;
-        rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, words, (uint64_t)N, words,
-                      (uint32_t)(BLOCK_K * q->bits / 32), BLOCK_N, CU_TENSOR_MAP_SWIZZLE_NONE);
+        const uint32_t step_words = (uint32_t)(BLOCK_K * q->bits / 32);        // 8 (4-bit) or 16 (8-bit) words per K step
+        if (tsa)   // one box per chunk; rows of 32 or 64 bytes, swizzled so that a thread per row reads without bank conflicts
+            rc = make_map3(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, (uint64_t)(K / BLOCK_K), (uint64_t)N, words, BLOCK_N,
+                           (uint32_t)p.ks, step_words, q->bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
+        else
+            rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, words, (uint64_t)N, words, step_words, BLOCK_N,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return rc;
     }
 
-    if (dtype == BI_BF16) {
-        if (!quant) return launch_t<__nv_bfloat16, 0>(mw, mx, p, st);
-        return q->bits == 4 ? launch_t<__nv_bfloat16, 4>(mw, mx, p, st) : launch_t<__nv_bfloat16, 8>(mw, mx, p, st);
-    }
-    if (!quant) return launch_t<__half, 0>(mw, mx, p, st);
-    return q->bits == 4 ? launch_t<__half, 4>(mw, mx, p, st) : launch_t<__half, 8>(mw, mx, p, st);
+#define BI_TC_LAUNCH(TT)                                                                                          \
+    do {                                                                                                          \
+        if (!quant) return launch_t<TT, 0, false>(mw, mx, p, st);                                                 \
+        if (tsa) return q->bits == 4 ? launch_t<TT, 4, true>(mw, mx, p, st) : launch_t<TT, 8, true>(mw, mx, p, st); \
+        return q->bits == 4 ? launch_t<TT, 4, false>(mw, mx, p, st) : launch_t<TT, 8, false>(mw, mx, p, st);      \
+    } while (0)
+    if (dtype == BI_BF16) BI_TC_LAUNCH(__nv_bfloat16);
+    BI_TC_LAUNCH(__half);
+#undef BI_TC_LAUNCH
 }
 
 }  // namespace bi

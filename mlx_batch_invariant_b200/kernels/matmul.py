@@ -18,11 +18,17 @@ from ._util import adopt, dtype_code, give_back, require_cuda, rows_16b
 
 GROUP_K = 256
 
-_PATHS = {"auto": _lib.PATH_AUTO, "split": _lib.PATH_SPLIT, "fused": _lib.PATH_FUSED}
+_PATHS = {"auto": _lib.PATH_AUTO, "split": _lib.PATH_SPLIT, "fused": _lib.PATH_FUSED, "fold": _lib.PATH_SPLIT_FOLD}
 
 
-def _workspace(nbytes: int, dev: torch.device) -> torch.Tensor | None:
-    return torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+def _launch_shape(path: str, batch_tile: int | None, M: int, N: int, K: int, ws_bytes_auto: int, dev: torch.device):
+    """(path word, workspace tensor or None, workspace bytes) for a call. The workspace is the stream's
+    persistent one, whose head holds the zeroed arrival counters of the in-kernel fold."""
+    G = (K + GROUP_K - 1) // GROUP_K
+    nbytes = ws_bytes_auto if path in ("auto", "fused") else _lib.COUNTER_BYTES + G * M * N * 4
+    word = _PATHS[path] | _lib.WS_ZEROED | (_lib.batch_tile(batch_tile) if batch_tile else 0)
+    ws = _lib.matmul_workspace(dev, nbytes) if nbytes else None
+    return word, ws, (ws.numel() if ws is not None else 0)
 
 
 def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
@@ -33,12 +39,13 @@ def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
             and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
 
 
-def batch_invariant_matmul(a, b, *, path: str = "auto"):
+def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None):
     """``a @ b`` with a batch-invariant reduction order.
 
     ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
     view is fine). fp32 accumulation; the output dtype is the promoted input dtype.
-    ``path`` ("auto", "split", "fused") forces a launch shape; all give the same bits.
+    ``path`` ("auto", "split", "fused", "fold") and ``batch_tile`` (16, 32, 64, 128 batch rows per tile)
+    force a launch shape; all give the same bits.
     """
     at, foreign = adopt(a)
     bt, _ = adopt(b)
@@ -66,11 +73,9 @@ def batch_invariant_matmul(a, b, *, path: str = "auto"):
         a2 = rows_16b(a2)
     out = torch.empty((M, N), dtype=out_dtype, device=dev)
     lib = _lib.load()
-    G = (K + GROUP_K - 1) // GROUP_K
-    nbytes = G * M * N * 4 if path == "split" else lib.bi_matmul_workspace_bytes(M, N, K, code)
-    ws = _workspace(nbytes, dev)
     with torch.cuda.device(dev):
+        word, ws, nbytes = _launch_shape(path, batch_tile, M, N, K, lib.bi_matmul_workspace_bytes(M, N, K, code), dev)
         _lib.check(lib.bi_matmul(a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
                                  a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code,
-                                 _PATHS[path], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+                                 word, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
     return give_back(out.reshape(*lead, N), a, foreign)

@@ -16,7 +16,7 @@ import torch
 
 from .. import _lib
 from ._util import adopt, dtype_code, give_back, require_cuda, rows_16b
-from .matmul import GROUP_K, _PATHS, _workspace
+from .matmul import _launch_shape
 
 SUPPORTED_BITS = (4, 8)
 SUPPORTED_GROUPS = (32, 64, 128)
@@ -38,7 +38,13 @@ def supports(x, w, scales, biases, transpose, group_size, bits, mode) -> bool:
     )
 
 
-def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, bits: int, path: str = "auto"):
+_STAGES = {None: 0, "smem": _lib.QMM_STAGE_SMEM, "tmem": _lib.QMM_STAGE_TMEM}
+
+
+def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, bits: int, path: str = "auto",
+                                     batch_tile: int | None = None, stage: str | None = None):
+    """``x @ dequant(w).T``. ``path`` / ``batch_tile`` force a launch shape as for the dense matmul; ``stage``
+    ("smem", "tmem") forces how the dequantized weight reaches the tensor core. All give the same bits."""
     xt, foreign = adopt(x)
     wt, st, bt = adopt(w)[0], adopt(scales)[0], adopt(biases)[0]
     dev = require_cuda(xt, wt, st, bt)
@@ -60,11 +66,9 @@ def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, b
     wt = wt.contiguous()
     out = torch.empty((M, N), dtype=dt, device=dev)
     lib = _lib.load()
-    G = (K + GROUP_K - 1) // GROUP_K
-    nbytes = G * M * N * 4 if path == "split" else lib.bi_qmm_workspace_bytes(M, N, K, code)
-    ws = _workspace(nbytes, dev)
     with torch.cuda.device(dev):
+        word, ws, nbytes = _launch_shape(path, batch_tile, M, N, K, lib.bi_qmm_workspace_bytes(M, N, K, code), dev)
         _lib.check(lib.bi_qmm(x2.data_ptr(), wt.data_ptr(), st.data_ptr(), bt.data_ptr(), out.data_ptr(),
                               _lib.ptr(ws), nbytes, M, N, K, x2.stride(0) if M > 1 else K, group_size, bits, code,
-                              _PATHS[path], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+                              word | _STAGES[stage], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
     return give_back(out.reshape(*lead, N), x, foreign)

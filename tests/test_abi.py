@@ -64,24 +64,26 @@ def test_validation_status_codes(call, code):
 
 def test_workspace_sizes():
     L = _lib.load()
-    assert L.bi_matmul_workspace_bytes(1, 4096, 4096, _lib.BI_BF16) == 16 * 1 * 4096 * 4
+    assert L.bi_matmul_workspace_bytes(1, 4096, 4096, _lib.BI_BF16) == _lib.COUNTER_BYTES + 16 * 1 * 4096 * 4
     assert L.bi_matmul_workspace_bytes(4096, 4096, 4096, _lib.BI_BF16) == 0   # fused: no scratch
     assert L.bi_matmul_workspace_bytes(8, 4096, 256, _lib.BI_BF16) == 0       # one K group
     assert L.bi_attn_decode_workspace_bytes(2, 32, 257, 128, 256) == 2 * 32 * 2 * (128 + 2) * 4
 
 
 def test_workspace_sizes_follow_the_auto_launch_shape():
-    """bi_matmul_workspace_bytes covers whatever AUTO may pick: ceil(K/256) * M * N * 4 bytes when the K groups
-    may be spread over CTAs (few tiles and M <= 64, or partials of at most 80 MB), nothing otherwise."""
+    """bi_matmul_workspace_bytes covers whatever AUTO may pick: the counter block plus ceil(K/256) * M * N * 4
+    bytes when the K groups may be spread over CTAs, nothing when the call is sure to fold in place (enough
+    tiles at some batch-tile height, or partials too large)."""
     L = _lib.load()
     f = L.bi_matmul_workspace_bytes
-    assert f(1, 4096, 4096, _lib.BI_BF16) == 16 * 1 * 4096 * 4
-    assert f(64, 4096, 14336, _lib.BI_BF16) == 56 * 64 * 4096 * 4
-    assert f(128, 4096, 4096, _lib.BI_BF16) == 16 * 128 * 4096 * 4          # 32 tiles, 33.5 MB of partials: split
-    assert f(256, 4096, 4096, _lib.BI_BF16) == 16 * 256 * 4096 * 4
-    assert f(512, 4096, 4096, _lib.BI_BF16) == 0                            # 134 MB of partials: fused
+    CB = _lib.COUNTER_BYTES
+    assert f(1, 4096, 4096, _lib.BI_BF16) == CB + 16 * 1 * 4096 * 4
+    assert f(64, 4096, 14336, _lib.BI_BF16) == CB + 56 * 64 * 4096 * 4
+    assert f(128, 4096, 4096, _lib.BI_BF16) == 0                            # 32-row batch tiles make 128 tiles: fused
+    assert f(256, 4096, 4096, _lib.BI_BF16) == 0                            # 64-row batch tiles make 128 tiles: fused
+    assert f(512, 4096, 4096, _lib.BI_BF16) == 0
     assert f(128, 28672, 4096, _lib.BI_BF16) == 0                           # 224 tiles fill the GPU: fused
     assert f(128, 4096, 14336, _lib.BI_BF16) == 0                           # 117 MB of partials: fused
     assert f(64, 4096, 256, _lib.BI_BF16) == 0                              # one K group: nothing to fold
-    assert L.bi_qmm_workspace_bytes(16, 14336, 4096, _lib.BI_BF16) == 16 * 16 * 14336 * 4
+    assert L.bi_qmm_workspace_bytes(16, 14336, 4096, _lib.BI_BF16) == CB + 16 * 16 * 14336 * 4
     assert f(0, 4096, 4096, _lib.BI_BF16) == 0

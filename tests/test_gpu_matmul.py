@@ -94,6 +94,59 @@ def test_row_position_independence(bi, dt):
             assert R.bits_of(out[pos:pos + 1]) == want, (pos, path)
 
 
+# Batch sizes that make the kernel issue every MMA width it can (the instruction's N is the batch rows of a
+# tile rounded up to 16: 16, 32, ..., 128) and that sit on either side of every 16-row boundary.
+EVERY_WIDTH = [1, 8, 9, 16, 17, 32, 33, 48, 49, 64, 65, 80, 81, 96, 97, 112, 113, 127, 128, 129]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_every_mma_width_gives_the_batch1_bits(bi, dt):
+    """A row's bits at every batch size from 1 to 129, in the first and in the last row of the batch, through
+    the split, fused and in-kernel-fold launch shapes, equal its bits alone: an accumulator column depends on
+    its own batch row only, whatever width the instruction was issued with."""
+    N, K = 384, 1024
+    x, w = xw(129, N, K, dt, 5)
+    xc, wc = x.cuda(), w.cuda()
+    want = R.bits_of(bi.batch_invariant_matmul(xc[:1], wc.T))
+    for M in EVERY_WIDTH:
+        tail = xc[:M].clone()
+        tail[M - 1] = xc[0]
+        for path in ("split", "fused", "fold"):
+            assert R.bits_of(bi.batch_invariant_matmul(xc[:M], wc.T, path=path)[:1]) == want, (M, path)
+            assert R.bits_of(bi.batch_invariant_matmul(tail, wc.T, path=path)[M - 1:M]) == want, (M, path, "last row")
+    bi.check_device_status()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [40, 64, 129, 256])
+def test_batch_tile_height_moves_no_bit(bi, dt, M):
+    """The fused path may cut the batch into tiles of 16, 32, 64 or 128 rows (more tiles to fill the GPU); the
+    split path likewise. Every height gives the bits of the default launch."""
+    x, w = xw(M, 512, 768, dt, M)
+    xc, wc = x.cuda(), w.cuda()
+    want = R.bits_of(bi.batch_invariant_matmul(xc, wc.T))
+    for bt in (16, 32, 64, 128):
+        for path in ("fused", "split", "fold"):
+            assert R.bits_of(bi.batch_invariant_matmul(xc, wc.T, path=path, batch_tile=bt)) == want, (bt, path)
+    bi.check_device_status()
+
+
+def test_in_kernel_fold_leaves_its_counters_zero(bi):
+    """The fold's arrival counters live at the head of the stream's workspace and must be zero again after
+    every call, or the next call would fold early."""
+    from mlx_batch_invariant_b200 import _lib
+    x, w = xw(16, 4096, 4096, torch.bfloat16, 8)
+    xc, wc = x.cuda(), w.cuda()
+    want = R.bits_of(bi.batch_invariant_matmul(xc, wc.T, path="split"))
+    for _ in range(3):
+        assert R.bits_of(bi.batch_invariant_matmul(xc, wc.T, path="fold")) == want
+        assert R.bits_of(bi.batch_invariant_matmul(xc, wc.T)) == want          # AUTO folds in the kernel at M <= 16
+    torch.cuda.synchronize()
+    for ws in _lib._workspaces.values():
+        assert int(ws[:_lib.COUNTER_BYTES].view(torch.int32).abs().sum()) == 0
+    bi.check_device_status()
+
+
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 def test_strided_activation_and_leading_dims(bi, dt):
     x, w = xw(24, 256, 512, dt, 3)
@@ -132,6 +185,33 @@ def test_quantized_equals_dense_on_dequantized_weight(bi, dt, bits, gs):
     for path in ("split", "fused"):
         alt = bi.batch_invariant_quantized_matmul(x.cuda(), p.cuda(), s.cuda(), b.cuda(), group_size=gs, bits=bits, path=path)
         assert R.bits_of(alt) == R.bits_of(got)
+    bi.check_device_status()
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 64), (4, 32), (8, 128), (8, 32)])
+def test_quantized_every_width_and_both_stagings(bi, bits, gs):
+    """Quantized weights: every MMA width, both ways of staging the dequantized operand (shared memory, the
+    tile body; tensor memory, the streaming decode variant), every launch shape -- one set of bits, those of
+    the dense kernel on the dequantized weight."""
+    dt = torch.bfloat16
+    N, K = 264, 896                                     # a partial weight tile and a half-width last K group
+    p, s, b = quant_case(N, K, bits, gs, dt, bits + gs)
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(129, K, generator=g).to(dt).cuda()
+    pc, sc, bc = p.cuda(), s.cuda(), b.cuda()
+    wd = R.dequant(p, s, b, group_size=gs, bits=bits, dtype=dt).cuda()
+    q = lambda xx, **kw: bi.batch_invariant_quantized_matmul(xx, pc, sc, bc, group_size=gs, bits=bits, **kw)
+    want = R.bits_of(bi.batch_invariant_matmul(x[:1], wd.T))
+    for M in EVERY_WIDTH:
+        dense = bi.batch_invariant_matmul(x[:M], wd.T)
+        assert R.bits_of(dense[:1]) == want
+        stages = ("smem", "tmem") if M <= 64 else ("smem",)
+        for stage in stages:
+            for path in ("split", "fused", "fold"):
+                assert R.bits_of(q(x[:M], path=path, stage=stage)) == R.bits_of(dense), (M, stage, path)
+        assert R.bits_of(q(x[:M])) == R.bits_of(dense), (M, "auto")
+    for bt in (16, 32, 64):                             # tall batches cut into short tiles stream as well
+        assert R.bits_of(q(x, path="fused", batch_tile=bt, stage="tmem")) == R.bits_of(bi.batch_invariant_matmul(x, wd.T)), bt
     bi.check_device_status()
 
 
