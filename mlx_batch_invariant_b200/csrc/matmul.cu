@@ -10,15 +10,17 @@ namespace {
 
 constexpr int64_t SPLIT_M_MAX = 64;             // up to here the CUDA-core path may split; the tensor-core path always may
 constexpr int64_t SPLIT_PARTIAL_MAX = 80 << 20;  // beyond 64 rows: only while the fp32 partials stay L2-sized
-constexpr int64_t FOLD_M_MAX = 16;              // in-kernel fold of the split path: the last CTA of a tile reads G * M * 128 partials
+constexpr int64_t FOLD_M_MAX = 0;               // AUTO never folds in the kernel: the fence / count / read-back chain of every unit measured slower than the second launch (M = 1: 16.4 us against 12.6 us)
 constexpr size_t COUNTER_BYTES = BI_MATMUL_COUNTER_BYTES;
 
 int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 
 // AUTO launch shape for the tensor-core path. Fused needs enough (weight tile, batch tile) pairs to fill the
 // GPU; cutting the batch into shorter tiles makes more of them at the price of re-reading the weight tile
-// through L2 once per batch tile. Where even 16-row batch tiles are too few, or K is so long that one CTA
-// would stream megabytes of weights alone, the K groups are spread over CTAs instead (split).
+// through L2 once per batch tile, which pays down to 32-row tiles (measured at N = K = 4096: M = 256 fused in
+// 64-row tiles 19.7 us against 30.3 us split; M = 128 in 32-row tiles 17.4 against 17.9 us; M = 64 in 16-row
+// tiles 14.8 against 14.5 us). Below that the K groups are spread over CTAs (split) while the fp32 partials
+// stay L2-sized.
 TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
     TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO};
     const int64_t G = ngroups(K);
@@ -27,9 +29,8 @@ TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
     int bm_fill = 0;                               // tallest batch tile that still fills the GPU
     for (int bm = 128; bm >= 16; bm >>= 1)
         if (nt * ((M + bm - 1) / bm) >= fill) { bm_fill = bm; break; }
-    if (G <= 1) { sh.bm = bm_fill ? bm_fill : 16; return sh; }
+    if (G <= 1 || bm_fill >= 32) { sh.bm = bm_fill ? bm_fill : 16; return sh; }
     const bool partials_ok = M <= SPLIT_M_MAX || G * M * N * (int64_t)sizeof(float) <= SPLIT_PARTIAL_MAX;
-    if (bm_fill && (K <= 8192 || !partials_ok)) { sh.bm = bm_fill; return sh; }
     if (partials_ok) { sh.split = true; return sh; }
     sh.bm = bm_fill ? bm_fill : 16;
     return sh;

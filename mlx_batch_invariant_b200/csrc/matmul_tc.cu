@@ -62,9 +62,9 @@ constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BLOCK_N * BLOCK_K * 2;
 constexpr int TMEM_COLS = 512;
 // Tensor-memory columns: accumulator 0 at 0, accumulator 1 at acc_stride, the fused path's running total at
-// 2 * acc_stride (acc_stride = 128; 64 in the streaming variant, whose batch tile is at most 64 rows), and in
-// the streaming variant the weight-operand ring from column 256: 2 chunks x 4 K steps x 32 columns.
-constexpr int TMEM_A_COL0 = 256;
+// 2 * acc_stride (acc_stride = 128; 64 or 32 in the streaming variant, whose batch tile is at most 64 rows), and
+// in the streaming variant the weight-operand ring from column a_col0: w_slots chunks x 4 K steps x 32 columns
+// (two chunks from column 256; three from column 128 when the batch tile is at most 32 rows).
 constexpr int TMEM_A_STEP = BLOCK_K / 2;   // columns of one K step of the weight operand (two 16-bit values per column)
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 #ifndef BI_EPI_SLEEP_NS
@@ -91,9 +91,11 @@ constexpr int TSA_SMEM_CAP = 164 * 1024;   // leaves the L1 its share: the strea
 //                                         valid (unread-result) memory.
 //   W ring     dense: load_slots x ks x 16 KB (TMA)   quantized tile body: w_slots x ks x 16 KB (dequantizers)
 //              streaming: none (the operand lives in tensor memory)
-//   raw ring   quantized only: load_slots x ks x RAW_BYTES packed codes (TMA; no swizzle for the tile
-//              body, 32- or 64-byte swizzle for the streaming variant so that a thread per row reads
-//              its 16-byte pieces without bank conflicts)
+//   raw ring   quantized only: load_slots x ks x RAW_BYTES packed codes (TMA). A chunk's codes arrive as one
+//              or two boxes of 128 weight rows x raw_span bytes (raw_span = the chunk's bytes of a row, at
+//              most 128), swizzled so that threads reading one 16-byte piece per row meet no bank
+//              conflict. The box is as wide as the chunk, not as a K step: the TMA unit and the memory
+//              system work per row, and 32-byte rows streamed at a twentieth of the rate of 128-byte rows.
 //   barriers
 struct Params {
     void* out;          // [M, N] in T (fused)
@@ -115,6 +117,10 @@ struct Params {
     int w_slots;        // depth of the dequantized-weight ring (quantized), in chunks
     int w_ring_slots;   // slots of the ring the MMA reads weights from (w_slots, or load_slots when dense)
     int acc_stride;     // tensor-memory columns between the two accumulators
+    int a_col0;         // streaming variant: first tensor-memory column of the weight-operand ring
+    int uniform;        // every chunk is a whole K group (K % 256 == 0 and four K steps per chunk)
+    int raw_span;       // quantized: bytes of one weight row in one box of packed codes (32, 64 or 128)
+    int raw_boxes;      // quantized: boxes of packed codes per chunk (1 or 2)
     int gs;
     long long units;
 };
@@ -166,6 +172,16 @@ template <> struct Pack2<__half> {
         return *reinterpret_cast<uint32_t*>(&v);
     }
 };
+
+// Byte offset, inside a chunk's packed codes, of 16-byte piece `piece` of weight row `row` (pieces count along the
+// row's bytes of the chunk). The codes lie as boxes of 128 rows x span bytes under the TMA swizzle of that span:
+// the piece index inside a span is XORed with bits [7, 7 + log2(span / 16)) of the byte address.
+__device__ __forceinline__ uint32_t raw_piece_offset(int row, int piece, int span) {
+    const int per = span >> 4;                         // pieces per row of one box: 2, 4 or 8
+    const int box = piece / per, pb = piece - box * per;
+    const int sw = ((row * span) >> 7) & (per - 1);
+    return (uint32_t)(box * (BLOCK_N * span) + row * span + ((pb ^ sw) << 4));
+}
 
 // Eight consecutive codes -> eight T values, one 16-byte swizzle chunk.
 //   value = T(fma(float(code), scale, bias))   fp32 fma, one rounding.
@@ -263,27 +279,22 @@ struct ChunkIter {
     }
 };
 
-// One weight row's 64 codes of a K step -> 32 packed pairs of T, written to the row's tensor-memory lane at
-// columns taddr .. taddr+31 (column c holds elements 2c and 2c+1 of the row, low half first) in two stores of
-// 16 columns. `raw` is the K step's tile of packed codes as the swizzled TMA box left it; (s2a, b2a) apply to
-// codes 0..31, (s2b, b2b) to codes 32..63.
+// One weight row's 64 codes of K step `kstep` of a chunk -> 32 packed pairs of T, written to the row's
+// tensor-memory lane at columns taddr .. taddr+31 (column c holds elements 2c and 2c+1 of the row, low half
+// first) in two stores of 16 columns. `raw` is the chunk's packed codes as the TMA boxes left them (rows of 128
+// bytes, 128-byte swizzle); (s2a, b2a) apply to codes 0..31, (s2b, b2b) to codes 32..63.
 template <typename T, int QBITS>
-__device__ __forceinline__ void dequant_row64_to_tmem(const uint8_t* raw, int row, uint64_t s2a, uint64_t b2a, uint64_t s2b,
-                                                      uint64_t b2b, uint32_t taddr) {
-    constexpr int ROW_BYTES = BLOCK_K * QBITS / 8;       // 32 (4-bit) or 64 (8-bit)
-    constexpr int PIECES = ROW_BYTES / 16;               // 16-byte pieces per row
+__device__ __forceinline__ void dequant_row64_to_tmem(const uint8_t* raw, int row, int kstep, uint64_t s2a, uint64_t b2a,
+                                                      uint64_t s2b, uint64_t b2b, uint32_t taddr) {
+    constexpr int PIECES = BLOCK_K * QBITS / 8 / 16;     // 16-byte pieces behind 64 codes: 2 (4-bit) or 4 (8-bit)
     constexpr int HP = PIECES / 2;                       // pieces behind 32 codes
-    // TMA swizzle: the 16-byte piece index is XORed with address bits [7, 7 + log2(PIECES))
-    const int sw = QBITS == 4 ? ((row >> 2) & 1) : ((row >> 1) & 3);
-    const uint8_t* rp = raw + row * ROW_BYTES;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const uint64_t s2 = h ? s2b : s2a, b2 = h ? b2b : b2a;
         uint32_t o[16];
 #pragma unroll
         for (int cc = 0; cc < HP; ++cc) {
-            const int c = h * HP + cc;
-            const uint4 q = *reinterpret_cast<const uint4*>(rp + ((c ^ sw) << 4));
+            const uint4 q = *reinterpret_cast<const uint4*>(raw + raw_piece_offset(row, kstep * PIECES + h * HP + cc, 128));
             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
             if (QBITS == 4) {
 #pragma unroll
@@ -321,7 +332,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t bar_base = raw_ring + (uint32_t)(LS * KS) * C::RAW_BYTES;
     auto x_tile = [&](int l, int j) { return smem_base + (uint32_t)(l * KS + j) * p.x_bytes; };
     auto w_tile = [&](int w, int j) { return w_ring + (uint32_t)(w * KS + j) * W_TILE_BYTES; };
-    auto raw_tile = [&](int l, int j) { return raw_ring + (uint32_t)(l * KS + j) * C::RAW_BYTES; };
+    auto raw_chunk = [&](int l) { return raw_ring + (uint32_t)(l * KS) * C::RAW_BYTES; };   // packed codes of slot l
     auto bar_lfull = [&](int l) { return bar_base + 8u * l; };                    // TMA landed (slot l)
     auto bar_wfull = [&](int w) { return bar_base + 8u * (MAX_SLOTS + w); };      // dequantized chunk ready
     auto bar_done = [&](int d) { return bar_base + 8u * (2 * MAX_SLOTS + d); };   // MMAs of a chunk complete
@@ -370,14 +381,17 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (warp == WARP_TMA) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop (warp-uniform control flow and address arithmetic), one elected lane issues.
+        {
+            const bool leader = ptx::elect_one();
             // The TMA unit's cost is per instruction (a few hundred cycles each, whatever the box holds), so
             // with box3d one box brings all K steps of a chunk: the tensor map is a 3-D view
             // [K/64 blocks][rows][64 elements] whose box lands as consecutive K-step tiles. K steps of the
             // box that lie beyond K are zero-filled and still count towards the barrier's bytes.
             const uint32_t xb = (uint32_t)p.x_rows * BLOCK_K * 2;
-            const uint32_t wb = QBITS ? (uint32_t)C::RAW_BYTES : (uint32_t)W_TILE_BYTES;
-            const bool w3d = p.box3d && (!QBITS || TSA);
+            const uint32_t wb = (uint32_t)W_TILE_BYTES;
+            const uint32_t raw_box_bytes = (uint32_t)(BLOCK_N * p.raw_span);
+            const bool w3d = p.box3d && !QBITS;
             // Weight tiles go through L2 marked evict-first: they should not push the batch rows or the split
             // path's partials out (measured faster also where several batch tiles re-read a weight tile).
             const uint64_t w_policy = ptx::l2_policy_evict_first();
@@ -388,20 +402,28 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (it.ci >= LS && !wait_done(it.ci - LS, ROLE_TMA)) { ok = false; break; }
                 const int kc = it.ksteps();
                 const uint32_t bar = bar_lfull(l);
-                ptx::mbar_expect_tx(bar, xb * (uint32_t)(p.box3d ? KS : kc) + wb * (uint32_t)(w3d ? KS : kc));
-                const int n0 = it.n0(), m0 = it.m0();
-                if (w3d) ptx::tma_load_3d_hint(QBITS ? raw_tile(l, 0) : w_tile(l, 0), &tmap_w, 0, n0, it.k0() >> 6, bar, w_policy);
-                if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, it.k0() >> 6, bar);
-                if (!w3d || !p.box3d) {
-                    for (int j = 0; j < kc; ++j) {
-                        const int k0 = it.k0() + j * BLOCK_K;
-                        if (!w3d) {
-                            if (QBITS) ptx::tma_load_2d_hint(raw_tile(l, j), &tmap_w, k0 * QBITS / 32, n0, bar, w_policy);
-                            else ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
+                const uint32_t tx = xb * (uint32_t)(p.box3d ? KS : kc) +
+                                    (QBITS ? raw_box_bytes * (uint32_t)p.raw_boxes : wb * (uint32_t)(w3d ? KS : kc));
+                const int n0 = it.n0(), m0 = it.m0(), k0c = it.k0();
+                if (leader) {
+                    ptx::mbar_expect_tx(bar, tx);
+                    if (QBITS) {
+                        // the chunk's codes: whole boxes (columns past the end of a weight row are zero-filled)
+                        for (int b = 0; b < p.raw_boxes; ++b)
+                            ptx::tma_load_2d_hint(raw_chunk(l) + (uint32_t)b * raw_box_bytes, &tmap_w,
+                                                  k0c * QBITS / 32 + b * (p.raw_span >> 2), n0, bar, w_policy);
+                    }
+                    if (w3d) ptx::tma_load_3d_hint(w_tile(l, 0), &tmap_w, 0, n0, k0c >> 6, bar, w_policy);
+                    if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, k0c >> 6, bar);
+                    if ((!QBITS && !w3d) || !p.box3d) {
+                        for (int j = 0; j < kc; ++j) {
+                            const int k0 = k0c + j * BLOCK_K;
+                            if (!QBITS && !w3d) ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
+                            if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
                         }
-                        if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
                     }
                 }
+                __syncwarp();
             }
             if (!ok) {
                 // Let the copies already in flight land before the CTA goes away.
@@ -415,65 +437,123 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else if (warp == WARP_MMA) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            // The MMA's N is the batch rows that were loaded, rounded up to the 16 the instruction wants
-            // (columns past the loaded rows see whatever follows in the ring and are never read back; an
-            // accumulator column depends on its own batch row only, whatever N is).
-            const uint32_t mma_n = (uint32_t)((p.x_rows + 15) & ~15);
-            const uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((mma_n >> 3) << 17) |
-                                   ((uint32_t)(BLOCK_N >> 4) << 24);
-            int job = -1; bool ok = true;
-            uint32_t tmem_d = tmem_base;
-            for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
-                if (it.first_in_group()) {
-                    ++job;
-                    const int buf = job & 1;
-                    if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
-                    tmem_d = tmem_base + (uint32_t)(buf * p.acc_stride);
-                }
-                const int l = it.l, w = it.w;
-                const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
-                if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
+        // The whole warp runs the loop, so that control flow and descriptor arithmetic are warp-uniform (a
+        // single-lane branch forces them onto per-thread registers, each instruction waiting for the one
+        // before: measured ~200 cycles per MMA); one elected lane issues the MMAs and the commit.
+        const bool leader = ptx::elect_one();
+        constexpr uint32_t FMT = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+        // The MMA's N is the batch rows that were loaded, rounded up to the 16 the instruction wants
+        // (columns past the loaded rows see whatever follows in the ring and are never read back; an
+        // accumulator column depends on its own batch row only, whatever N is).
+        const uint32_t mma_n = (uint32_t)((p.x_rows + 15) & ~15);
+        const uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((mma_n >> 3) << 17) |
+                               ((uint32_t)(BLOCK_N >> 4) << 24);
+        // Operand descriptors: constant bits + the tile's shared address in 16-byte units. One K step of 64 is
+        // one tile further (W: 1024 units, x: x_bytes / 16), a UMMA K step of 16 elements +32 bytes = +2.
+        const uint64_t da0 = ptx::smem_desc_sw128(w_ring), db0 = ptx::smem_desc_sw128(smem_base);
+        const uint32_t xstep = (uint32_t)p.x_bytes >> 4;
+        constexpr uint32_t WSTEP = W_TILE_BYTES >> 4;
+        int job = -1; bool ok = true;
+        uint32_t tmem_d = tmem_base;
+        if (p.uniform) {
+            // Every chunk is one whole K group with its own accumulator: nothing to enumerate but ring positions.
+            const int nch = (ue - ub) * (p.split ? 1 : p.G);
+            int l = 0, w = 0, d = 0;
+            uint32_t lph = 0, wph = 0;
+            const int wring = QBITS ? WS : LS;
+            uint64_t db_c = db0;
+            uint64_t da_c = da0;
+            uint32_t ta_c = tmem_base + (uint32_t)p.a_col0;
+            for (int ci = 0; ci < nch && ok; ++ci) {
+                const int buf = ci & 1;
+                if (!wait_bounded(bar_tempty(buf), (uint32_t)((ci >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
+                tmem_d = tmem_base + (uint32_t)(buf * p.acc_stride);
+                if (!wait_bounded(QBITS ? bar_wfull(w) : bar_lfull(l), QBITS ? wph : lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
                 ptx::tc_fence_after();
-                const int kc = it.ksteps();
-                const int kend = min(p.K, (it.g + 1) * GROUP_K);
-                for (int j = 0; j < kc; ++j) {
-                    const int kleft = kend - (it.k0() + j * BLOCK_K);
-                    // one descriptor per operand and K step of 64; a UMMA K step of 16 elements is
-                    // +32 bytes, i.e. +2 in the descriptor's 16-byte address field
-                    const uint64_t db = ptx::smem_desc_sw128(x_tile(l, j));
-                    if constexpr (TSA) {
-                        // weight operand in tensor memory: a UMMA K step of 16 elements is 8 columns
-                        const uint32_t ta = tmem_base + (uint32_t)(TMEM_A_COL0 + (w * KS + j) * TMEM_A_STEP);
-                        if (kleft >= BLOCK_K) {
-                            if (it.c | j) ptx::umma_f16_ts_c<true>(tmem_d, ta, db, IDESC);
-                            else          ptx::umma_f16_ts_c<false>(tmem_d, ta, db, IDESC);
+                if (leader) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t db = db_c + (uint64_t)((uint32_t)j * xstep);
+                        if constexpr (TSA) {
+                            const uint32_t ta = ta_c + (uint32_t)(j * TMEM_A_STEP);
+                            if (j == 0) ptx::umma_f16_ts_c<false>(tmem_d, ta, db, IDESC);
+                            else        ptx::umma_f16_ts_c<true>(tmem_d, ta, db, IDESC);
                             ptx::umma_f16_ts_c<true>(tmem_d, ta + 8, db + 2, IDESC);
                             ptx::umma_f16_ts_c<true>(tmem_d, ta + 16, db + 4, IDESC);
                             ptx::umma_f16_ts_c<true>(tmem_d, ta + 24, db + 6, IDESC);
                         } else {
-                            const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
-                            for (int kk = 0; kk < nsteps; ++kk)
-                                ptx::umma_f16_ts(tmem_d, ta + 8 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
-                        }
-                    } else {
-                        const uint64_t da = ptx::smem_desc_sw128(QBITS ? w_tile(w, j) : w_tile(l, j));
-                        if (kleft >= BLOCK_K) {
-                            if (it.c | j) ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
-                            else          ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                            const uint64_t da = da_c + (uint64_t)(j * WSTEP);
+                            if (j == 0) ptx::umma_f16_c<false>(tmem_d, da, db, IDESC);
+                            else        ptx::umma_f16_c<true>(tmem_d, da, db, IDESC);
                             ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
                             ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
                             ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
-                        } else {
-                            const int nsteps = (kleft + UMMA_K - 1) / UMMA_K;
-                            for (int kk = 0; kk < nsteps; ++kk)
-                                ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                        }
+                    }
+                    ptx::umma_commit(bar_done(d));
+                }
+                __syncwarp();
+                if (++d == MAX_SLOTS) d = 0;
+                if (++l == LS) { l = 0; lph ^= 1u; }
+                if (++w == wring) { w = 0; wph ^= 1u; }
+                db_c = db0 + (uint64_t)((uint32_t)(l * 4) * xstep);
+                da_c = da0 + (uint64_t)((uint32_t)((QBITS ? w : l) * 4) * WSTEP);
+                ta_c = tmem_base + (uint32_t)(p.a_col0 + w * 4 * TMEM_A_STEP);
+            }
+        }
+        for (ChunkIter it(p, ub, ue); !p.uniform && it.valid() && ok; it.next()) {
+            if (it.first_in_group()) {
+                ++job;
+                const int buf = job & 1;
+                if (!wait_bounded(bar_tempty(buf), (uint32_t)((job >> 1) & 1) ^ 1u, ctl, ROLE_MMA, 32 + buf)) { ok = false; break; }
+                tmem_d = tmem_base + (uint32_t)(buf * p.acc_stride);
+            }
+            const int l = it.l, w = it.w;
+            const uint32_t ready = QBITS ? bar_wfull(w) : bar_lfull(l);
+            if (!wait_bounded(ready, QBITS ? it.wph : it.lph, ctl, ROLE_MMA, QBITS ? 8 + w : l)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const int kc = it.ksteps();
+            const uint64_t db_c = db0 + (uint64_t)((uint32_t)(l * KS) * xstep);
+            const uint64_t da_c = da0 + (uint64_t)((uint32_t)((QBITS ? w : l) * KS) * WSTEP);
+            const uint32_t ta_c = tmem_base + (uint32_t)(p.a_col0 + w * KS * TMEM_A_STEP);
+            (void)da_c; (void)ta_c;
+            if (p.box3d) {
+                // K % 64 == 0: every K step of the chunk is whole -- four MMAs each, offsets known at compile time
+#pragma unroll 1
+                for (int j = 0; j < kc; ++j) {
+                    const uint64_t db = db_c + (uint64_t)((uint32_t)j * xstep);
+                    const uint32_t acc0 = (it.c | j) ? 1u : 0u;
+                    if constexpr (TSA) {
+                        const uint32_t ta = ta_c + (uint32_t)(j * TMEM_A_STEP);
+                        if (leader) {
+                            ptx::umma_f16_ts(tmem_d, ta, db, IDESC, acc0);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 8, db + 2, IDESC);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 16, db + 4, IDESC);
+                            ptx::umma_f16_ts_c<true>(tmem_d, ta + 24, db + 6, IDESC);
+                        }
+                    } else {
+                        const uint64_t da = da_c + (uint64_t)((uint32_t)j * WSTEP);
+                        if (leader) {
+                            ptx::umma_f16(tmem_d, da, db, IDESC, acc0);
+                            ptx::umma_f16_c<true>(tmem_d, da + 2, db + 2, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 4, db + 4, IDESC);
+                            ptx::umma_f16_c<true>(tmem_d, da + 6, db + 6, IDESC);
                         }
                     }
                 }
-                ptx::umma_commit(bar_done(it.d));
+            } else {
+                const int kend = min(p.K, (it.g + 1) * GROUP_K);
+                for (int j = 0; j < kc; ++j) {
+                    const int kleft = kend - (it.k0() + j * BLOCK_K);
+                    const int nsteps = kleft >= BLOCK_K ? BLOCK_K / UMMA_K : (kleft + UMMA_K - 1) / UMMA_K;
+                    const uint64_t db = db_c + (uint64_t)((uint32_t)j * xstep);
+                    const uint64_t da = da_c + (uint64_t)((uint32_t)j * WSTEP);
+                    for (int kk = 0; kk < nsteps; ++kk)
+                        if (leader) ptx::umma_f16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (it.c | j | kk) ? 1u : 0u);
+                }
             }
+            if (leader) ptx::umma_commit(bar_done(it.d));
+            __syncwarp();
         }
     } else if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4) {
         // ------------------------------------------------------------ epilogue
@@ -491,6 +571,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             return r;
         };
         T* out = static_cast<T*>(p.out);
+        float small_total[8];                                        // running totals of a tile of at most 8 batch rows (fused)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) small_total[j] = 0.0f;
         for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
             if (it.first_in_group()) ++job;
             if (!it.last_in_group()) continue;
@@ -503,7 +586,35 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int ncols = min(p.bm, p.M - m0);
             const uint32_t acc = lane_base + (uint32_t)(buf * p.acc_stride);
             const bool first = g == 0, last = g == p.G - 1;
-            if (p.split) {
+            if (ncols <= 8) {
+                // Few batch rows (decode): a narrow accumulator read, and in the fused shape the running totals
+                // stay in registers from group to group -- no round trip through tensor memory.
+                {
+                    constexpr int W = 8;
+                    uint32_t v[W];
+                    ptx::tmem_ld_32x8(acc, v);
+                    ptx::tmem_ld_wait();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar_tempty(buf));          // the accumulator is in registers
+                    if (p.split) {
+                        if (n < p.N) {
+                            float* dst = p.part + ((long long)g * p.M + m0) * p.N + n;
+#pragma unroll
+                            for (int j = 0; j < W; ++j)
+                                if (j < ncols) dst[(long long)j * p.N] = __uint_as_float(v[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < W; ++j) small_total[j] = add_rn(first ? 0.0f : small_total[j], __uint_as_float(v[j]));
+                        if (last && n < p.N) {
+#pragma unroll
+                            for (int j = 0; j < W; ++j)
+                                if (j < ncols) out[(long long)(m0 + j) * p.N + n] = Cvt<T>::down(small_total[j]);
+                        }
+                    }
+                }
+            } else if (p.split) {
                 // A TMEM load queues behind the MMAs already issued for the next unit, so the loads of two
                 // column blocks go out together and pay that wait once (the streaming variant, short of
                 // registers with its sixteen dequantizer warps, takes one block at a time).
@@ -535,41 +646,41 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         }
                     }
                 }
-                if (p.counters) {
-                    // In-kernel fold. Every thread's partial stores are fenced device-wide, the four warps meet,
-                    // one thread counts this unit in; the CTA that counts in last (all G partials of the tile are
-                    // then visible) folds them in ascending g and writes the output. The counter goes back to 0.
+            }
+            if (p.split && p.counters) {
+                // In-kernel fold. Every thread's partial stores are fenced device-wide, the four warps meet,
+                // one thread counts this unit in; the CTA that counts in last (all G partials of the tile are
+                // then visible) folds them in ascending g and writes the output. The counter goes back to 0.
+                __threadfence();
+                if (!epi_sync()) { ok = false; break; }
+                if (warp == WARP_EPI0 && lane == 0) {
+                    unsigned* ctr = p.counters + ((long long)it.nt * p.m_tiles + it.mt);
+                    const unsigned old = atomicAdd(ctr, 1u);
+                    const int mine = old == (unsigned)p.G - 1u;
+                    if (mine) atomicExch(ctr, 0u);
+                    *fold_flag = mine;
+                }
+                if (!epi_sync()) { ok = false; break; }
+                if (*fold_flag) {
                     __threadfence();
-                    if (!epi_sync()) { ok = false; break; }
-                    if (warp == WARP_EPI0 && lane == 0) {
-                        unsigned* ctr = p.counters + ((long long)it.nt * p.m_tiles + it.mt);
-                        const unsigned old = atomicAdd(ctr, 1u);
-                        const int mine = old == (unsigned)p.G - 1u;
-                        if (mine) atomicExch(ctr, 0u);
-                        *fold_flag = mine;
-                    }
-                    if (!epi_sync()) { ok = false; break; }
-                    if (*fold_flag) {
-                        __threadfence();
-                        if (n < p.N) {
-                            const long long gstride = (long long)p.M * p.N;
+                    if (n < p.N) {
+                        const long long gstride = (long long)p.M * p.N;
 #pragma unroll 1
-                            for (int mm = 0; mm < ncols; mm += 4) {
-                                const float* src = p.part + (long long)(m0 + mm) * p.N + n;
-                                float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        for (int mm = 0; mm < ncols; mm += 4) {
+                            const float* src = p.part + (long long)(m0 + mm) * p.N + n;
+                            float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
-                                for (int gg = 0; gg < p.G; ++gg) {
-                                    float v[4];
-#pragma unroll
-                                    for (int u = 0; u < 4; ++u)
-                                        v[u] = (mm + u < ncols) ? __ldcg(src + gg * gstride + (long long)u * p.N) : 0.0f;
-#pragma unroll
-                                    for (int u = 0; u < 4; ++u) tot[u] = add_rn(tot[u], v[u]);
-                                }
+                            for (int gg = 0; gg < p.G; ++gg) {
+                                float v[4];
 #pragma unroll
                                 for (int u = 0; u < 4; ++u)
-                                    if (mm + u < ncols) out[(long long)(m0 + mm + u) * p.N + n] = Cvt<T>::down(tot[u]);
+                                    v[u] = (mm + u < ncols) ? __ldcg(src + gg * gstride + (long long)u * p.N) : 0.0f;
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) tot[u] = add_rn(tot[u], v[u]);
                             }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (mm + u < ncols) out[(long long)(m0 + mm + u) * p.N + n] = Cvt<T>::down(tot[u]);
                         }
                     }
                 }
@@ -578,7 +689,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             // (16 in the streaming variant, which is short of registers).
             constexpr int EW = TSA ? 16 : 32;
 #pragma unroll 1
-            for (int c = 0; !p.split && c * EW < ncols; ++c) {  // warp-uniform trip count
+            for (int c = 0; !p.split && ncols > 8 && c * EW < ncols; ++c) {  // warp-uniform trip count
                 uint32_t v[EW], t[EW];
                 if constexpr (TSA) {
                     ptx::tmem_ld_32x16(acc + c * EW, v);
@@ -604,7 +715,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     else ptx::tmem_st_32x32(lane_base + tmem_total + c * EW, t);
                 }
             }
-            if (!p.split) {
+            if (!p.split && ncols > 8) {
                 if (!last) ptx::tmem_st_wait();
                 ptx::tc_fence_before();
                 __syncwarp();
@@ -614,8 +725,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (QBITS && !TSA && warp >= WARP_DEQ0) {
         // ------------------------------------------------------------ dequantizers (tile body)
         // 256 threads: thread t turns half a weight row (32 codes) of every K step into four
-        // 16-byte chunks of the swizzled tile. Two threads per row, so a warp reads 512 contiguous
-        // bytes of packed codes and its stores spread over all banks.
+        // 16-byte chunks of the swizzled tile. Two threads per row; its stores spread over all banks.
         constexpr int QB = QBITS ? QBITS : 4;
         constexpr int ROW_BYTES = BLOCK_K * QB / 8;     // packed bytes per weight row per K step
         constexpr int HALF_WORDS = ROW_BYTES / 8;       // 32-bit words behind 32 codes
@@ -692,11 +802,12 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const int qi = ((it.c * KS + j) * BLOCK_K + half * 32) >> gs_shift;  // index inside this K group
                 const float sc = entry(sw, qi), bs = entry(bw, qi);
                 const uint64_t s2 = ptx::pack2(sc, sc), b2 = ptx::pack2(bs, bs);
-                const uint4* raw = reinterpret_cast<const uint4*>(smem_gen + (raw_tile(l, j) - smem_base) + row * ROW_BYTES + half * (ROW_BYTES / 2));
+                const uint8_t* raw = smem_gen + (raw_chunk(l) - smem_base);
+                constexpr int HALF_PIECES = HALF_WORDS / 4;      // 16-byte pieces behind 32 codes: 1 (4-bit) or 2 (8-bit)
                 uint32_t rw[HALF_WORDS];
 #pragma unroll
-                for (int i = 0; i < HALF_WORDS / 4; ++i) {
-                    const uint4 q = raw[i];
+                for (int i = 0; i < HALF_PIECES; ++i) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(raw + raw_piece_offset(row, (j * 2 + half) * HALF_PIECES + i, p.raw_span));
                     rw[4 * i] = q.x; rw[4 * i + 1] = q.y; rw[4 * i + 2] = q.z; rw[4 * i + 3] = q.w;
                 }
                 uint8_t* wt = smem_gen + (w_tile(w, j) - smem_base) + row * 128;
@@ -753,7 +864,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         ChunkIter pf(p, ub, ue);
 #pragma unroll
         for (int i = 0; i < DEPTH; ++i) { fetch(pf, qs[i], qb[i]); if (pf.valid()) pf.next(); }
-        const uint32_t a_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)TMEM_A_COL0;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)p.a_col0;
         bool ok = true;
         for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
             const uint32_t sv = qs[0], bv = qb[0];
@@ -767,7 +878,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (jstep < it.ksteps()) {
                 ptx::tc_fence_after();
                 const float s0 = to_f(sv & 0xffffu), s1 = to_f(sv >> 16), b0 = to_f(bv & 0xffffu), b1 = to_f(bv >> 16);
-                dequant_row64_to_tmem<T, QB>(smem_gen + (raw_tile(l, jstep) - smem_base), row, ptx::pack2(s0, s0), ptx::pack2(b0, b0),
+                dequant_row64_to_tmem<T, QB>(smem_gen + (raw_chunk(l) - smem_base), row, jstep, ptx::pack2(s0, s0), ptx::pack2(b0, b0),
                                              ptx::pack2(s1, s1), ptx::pack2(b1, b1),
                                              a_lane + (uint32_t)((w * KS + jstep) * TMEM_A_STEP));
                 ptx::tmem_st_wait();
@@ -931,14 +1042,21 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     bool tsa = quant && mr <= 64 && p.box3d && shape.stage != TcShape::STAGE_SMEM;
     if (quant && shape.stage == TcShape::STAGE_TMEM && !tsa)
         return fail(BI_ERR_UNSUPPORTED, "qmm: the tensor-memory staging needs a batch tile of at most 64 rows");
-    p.acc_stride = tsa ? 64 : BLOCK_M;
 
     if (!pick_rings(p, quant ? BLOCK_N * BLOCK_K * q->bits / 8 : 0, tsa)) {
         if (!tsa || shape.stage == TcShape::STAGE_TMEM || !pick_rings(p, BLOCK_N * BLOCK_K * q->bits / 8, false))
             return fail(BI_ERR_UNSUPPORTED, "matmul: no shared-memory configuration fits");
         tsa = false;
-        p.acc_stride = BLOCK_M;
     }
+    p.acc_stride = BLOCK_M;
+    if (tsa) {
+        // tensor-memory budget of the streaming variant: two accumulators + the running total, then the operand ring
+        const bool small = mr <= 32;
+        p.acc_stride = small ? 32 : 64;
+        p.a_col0 = small ? 128 : 256;
+        p.w_slots = p.w_ring_slots = small ? 3 : 2;
+    }
+    p.uniform = (K % GROUP_K == 0 && p.ks == 4) ? 1 : 0;
 
     const CUtensorMapDataType dt = dtype == BI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mw, mx;
@@ -957,14 +1075,15 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
         if (rc) return rc;
     }
     if (quant) {
+        // A chunk's codes of one weight row are ks * 64 * bits / 8 bytes: one box per 128 of them.
         const uint64_t words = (uint64_t)K * q->bits / 32;
-        const uint32_t step_words = (uint32_t)(BLOCK_K * q->bits / 32);        // 8 (4-bit) or 16 (8-bit) words per K step
-        if (tsa)   // one box per chunk; rows of 32 or 64 bytes, swizzled so that a thread per row reads without bank conflicts
-            rc = make_map3(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, (uint64_t)(K / BLOCK_K), (uint64_t)N, words, BLOCK_N,
-                           (uint32_t)p.ks, step_words, q->bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
-        else
-            rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, words, (uint64_t)N, words, step_words, BLOCK_N,
-                          CU_TENSOR_MAP_SWIZZLE_NONE);
+        const int chunk_row_bytes = p.ks * BLOCK_K * q->bits / 8;              // 32 .. 256
+        p.raw_span = chunk_row_bytes < 128 ? chunk_row_bytes : 128;
+        p.raw_boxes = chunk_row_bytes / p.raw_span;
+        const CUtensorMapSwizzle sw = p.raw_span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                    : (p.raw_span == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+        rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q->codes, words, (uint64_t)N, words, (uint32_t)(p.raw_span / 4),
+                      BLOCK_N, sw);
         if (rc) return rc;
     }
 

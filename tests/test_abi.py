@@ -80,6 +80,7 @@ def test_workspace_sizes_follow_the_auto_launch_shape():
     assert f(1, 4096, 4096, _lib.BI_BF16) == CB + 16 * 1 * 4096 * 4
     assert f(64, 4096, 14336, _lib.BI_BF16) == CB + 56 * 64 * 4096 * 4
     assert f(128, 4096, 4096, _lib.BI_BF16) == 0                            # 32-row batch tiles make 128 tiles: fused
+    assert f(96, 4096, 4096, _lib.BI_BF16) == CB + 16 * 96 * 4096 * 4       # 16-row tiles would be needed: split
     assert f(256, 4096, 4096, _lib.BI_BF16) == 0                            # 64-row batch tiles make 128 tiles: fused
     assert f(512, 4096, 4096, _lib.BI_BF16) == 0
     assert f(128, 28672, 4096, _lib.BI_BF16) == 0                           # 224 tiles fill the GPU: fused
