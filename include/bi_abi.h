@@ -171,6 +171,9 @@ int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int6
  *   q -> q_out[B, Hq, T, D] rotated with cos/sin tables fp32 [positions, D]    *
  *   (the two halves of a head share an angle); rotated k and plain v are       *
  *   written into the caches [*, Hkv, capacity, D] (element strides given).     *
+ *   `capacity` bounds the position (cache length and rows of the tables): a    *
+ *   token whose position falls outside writes nothing and stores               *
+ *   0x30000 | position into *status (see bi_read_device_status).               *
  * bi_swiglu: out[M, F] = T(silu(gu[:, :F]) * gu[:, F:]) for gu[M, 2F].         *
  * bi_add_rms_norm: the residual add in front of a norm, in one launch:         *
  *   sum_out[r, :] = T(x[r, :] + delta[r, :])  (fp32 add, one rounding: the      *
@@ -179,7 +182,8 @@ int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int6
  * ------------------------------------------------------------------------ */
 int bi_rope_append(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos0,
                    void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
-                   int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int dtype, void* stream);
+                   int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity,
+                   int32_t* status, int dtype, void* stream);
 
 int bi_swiglu(const void* gate_up, void* out, int64_t M, int64_t F, int dtype, void* stream);
 

@@ -48,7 +48,7 @@ SIGNATURES = {
     "bi_attn_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_void_p]),
     "bi_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                               c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+                               c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "bi_swiglu": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "bi_peer_alloc": (c_int, [ctypes.POINTER(c_void_p), c_size_t]),
     "bi_peer_free": (c_int, [c_void_p]),

@@ -12,8 +12,8 @@ Patched while the mode is on:
     modules call.
   * MLX, when ``mlx.core`` is importable: the six symbols the reference patches
     (``mx.matmul``, ``mx.addmm``, ``mx.quantized_matmul``, ``mx.fast.rms_norm``,
-    ``mx.fast.scaled_dot_product_attention``, ``mx.array.__matmul__``); arrays cross over
-    DLPack.
+    ``mx.fast.scaled_dot_product_attention``, ``mx.array.__matmul__``), through wrappers of
+    their own (``_mlx.py``): arrays cross over DLPack, and a fallback goes to the MLX stock op.
 Code that captured a stock callable before the block was entered bypasses the mode, as in
 the reference.
 """
@@ -56,18 +56,9 @@ def _mlx_patches():
         import mlx.core as mx
     except Exception:  # an MLX install that cannot initialise is the same as none
         return []
+    from . import _mlx
 
-    def _patched_array_matmul(self, other):
-        return ops.matmul(self, other)
-
-    return [
-        (mx, "matmul", ops.matmul),
-        (mx, "addmm", ops.addmm),
-        (mx, "quantized_matmul", ops.quantized_matmul),
-        (mx.fast, "rms_norm", ops.rms_norm),
-        (mx.fast, "scaled_dot_product_attention", ops.scaled_dot_product_attention),
-        (mx.array, "__matmul__", _patched_array_matmul),
-    ]
+    return _mlx.patches(mx)
 
 
 def _apply():

@@ -782,7 +782,8 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
     // With few units the GPU is short of independent key streams, so the heads of a kv head stop
     // sharing a stream (the rows are then re-read through L2) until there are enough.
     int GU = (G >= 4 && DL < 8) ? 4 : (G >= 2 ? 2 : 1);
-    const int64_t enough = 148 * 16;
+    const int64_t sms = sm_count();
+    const int64_t enough = sms * 16;
     while (GU > 1 && B * Hkv * ((G + GU - 1) / GU) * nsplit < enough) GU >>= 1;
     const int nchunk = (G + GU - 1) / GU;
     const int64_t units = B * Hkv * nchunk * nsplit;
@@ -801,7 +802,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
                             lay.sl % per16 == 0 && (32 * DL * sizeof(T)) % 16 == 0;
         const int nchunk4 = (G + 3) / 4;
         const int64_t streams = B * Hkv * nchunk4 * nsplit;
-        if (rows16 && streams < 148 * 24) {
+        if (rows16 && streams < sms * 24) {
             // few streams: one warp per stream, its octets on different heads
             using CW = DecWCfg<T, DL>;
             // Warps per CTA: the streams are dealt out so that every SM gets the same number of warps (CTAs land
@@ -812,7 +813,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             constexpr int MAXW = (SMEM_CAP / CW::WARP_BYTES) < DECW_WARPS ? (SMEM_CAP / CW::WARP_BYTES) : DECW_WARPS;
             int wpc = 1;
             for (int k = 1; k <= 64; ++k) {
-                wpc = (int)((streams + 148LL * k - 1) / (148LL * k));
+                wpc = (int)((streams + sms * k - 1) / (sms * k));
                 if (wpc <= MAXW) break;
             }
             if (wpc > MAXW) wpc = MAXW;
@@ -825,11 +826,14 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
 #define BI_DECW_LAUNCH(MW)                                                                                              \
     do {                                                                                                                \
         auto kern = decode_warp_stream_kernel<T, DL, MW>;                                                               \
-        static bool attr_set = false; /* per instantiation */                                                           \
-        if (!attr_set && MW * CW::WARP_BYTES > 40 * 1024) {                                                             \
+        static bool attr_set[64] = {false}; /* per instantiation and device: the attribute is per device */            \
+        int dev_ = 0;                                                                                                   \
+        cudaGetDevice(&dev_);                                                                                           \
+        if (dev_ < 0 || dev_ >= 64) dev_ = 0;                                                                           \
+        if (!attr_set[dev_] && MW * CW::WARP_BYTES > 40 * 1024) {                                                       \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, MW * CW::WARP_BYTES); \
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
-            attr_set = true;                                                                                            \
+            attr_set[dev_] = true;                                                                                      \
         }                                                                                                               \
         kern<<<(unsigned)blocksw, 32 * wpc, smem_w, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv, \
                                                           (int)L, lay, scale, split, nsplit, nchunk4);                  \

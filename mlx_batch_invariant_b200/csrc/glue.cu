@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
                                                           const float* __restrict__ sinT, const int64_t* __restrict__ pos0,
                                                           T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc,
                                                           int B, int Tn, int Hq, int Hkv, int D, int64_t c_sb, int64_t c_sh,
-                                                          int64_t c_sl) {
+                                                          int64_t c_sl, int64_t capacity, int32_t* status) {
     const int H = Hq + 2 * Hkv;
     const int64_t total = (int64_t)B * Tn * H * D;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -26,6 +26,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
     const int t = (int)(bt % Tn);
     const int b = (int)(bt / Tn);
     const int64_t p = pos0[0] + t;
+    // The position comes from device memory (a replayed graph advances it): a position outside the cache or
+    // the tables writes nothing and leaves a code in the status word instead.
+    if (p < 0 || p >= capacity) {
+        if (status) atomicCAS(status, 0, (int)(0x30000 | (int)(p & 0xffff)));
+        return;
+    }
     const float x = Cvt<T>::up(qkv[i]);
     if (h >= Hq + Hkv) {                                   // v: copied as is
         vc[(int64_t)b * c_sb + (int64_t)(h - Hq - Hkv) * c_sh + p * c_sl + d] = qkv[i];
@@ -58,10 +64,11 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T
 
 extern "C" int bi_rope_append(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos0,
                               void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
-                              int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int dtype, void* stream) {
+                              int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity,
+                              int32_t* status, int dtype, void* stream) {
     using namespace bi;
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_rope_append: dtype %d", dtype);
-    if (B < 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || D % 2) return fail(BI_ERR_BAD_ARG, "bi_rope_append: bad sizes");
+    if (B < 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || D % 2 || capacity <= 0) return fail(BI_ERR_BAD_ARG, "bi_rope_append: bad sizes");
     if (B == 0) return BI_OK;
     if (!qkv || !cos_table || !sin_table || !pos0 || !q_out || !k_cache || !v_cache) return fail(BI_ERR_BAD_ARG, "bi_rope_append: null pointer");
     const int64_t total = B * T * (Hq + 2 * Hkv) * D;
@@ -69,7 +76,7 @@ extern "C" int bi_rope_append(const void* qkv, const float* cos_table, const flo
     if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_rope_append: too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define BI_ROPE(TT) rope_append_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(qkv), cos_table, sin_table, pos0, \
-        static_cast<TT*>(q_out), static_cast<TT*>(k_cache), static_cast<TT*>(v_cache), (int)B, (int)T, (int)Hq, (int)Hkv, (int)D, cache_sb, cache_sh, cache_sl)
+        static_cast<TT*>(q_out), static_cast<TT*>(k_cache), static_cast<TT*>(v_cache), (int)B, (int)T, (int)Hq, (int)Hkv, (int)D, cache_sb, cache_sh, cache_sl, capacity, status)
     if (dtype == BI_F32) BI_ROPE(float); else if (dtype == BI_F16) BI_ROPE(__half); else BI_ROPE(__nv_bfloat16);
 #undef BI_ROPE
     return check_launch("bi_rope_append");

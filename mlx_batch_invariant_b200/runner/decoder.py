@@ -86,7 +86,8 @@ class KernelBackend(TorchGlue):
         qkv = qkv.contiguous()
         _lib.check(_lib.load().bi_rope_append(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos0.data_ptr(), q.data_ptr(),
                                               kc.data_ptr(), vc.data_ptr(), B, T, hq, hkv, D, kc.stride(0), kc.stride(1),
-                                              kc.stride(2), _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device)))
+                                              kc.stride(2), min(kc.shape[2], cos.shape[0]), _lib.status_word(qkv.device).data_ptr(),
+                                              _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device)))
         return q
 
     def swiglu(self, gu):
@@ -241,6 +242,14 @@ class ShardedDecoder:
             self._pg = PushGather(self.group, self.rank, self.world, self.dev, self.max_batch * widest * es)
         return self._pg
 
+    def check_capacity(self, batch: int, end: int) -> None:
+        """Raise before anything is launched if `batch` sequences of `end` tokens do not fit the KV cache and
+        the rotary tables (the kernels would otherwise be asked to write past them)."""
+        if batch > self.max_batch:
+            raise ValueError(f"batch {batch} exceeds the cache's max_batch={self.max_batch}")
+        if end > self.max_len:
+            raise ValueError(f"position {end} exceeds the cache's max_len={self.max_len}")
+
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, start: int) -> torch.Tensor:
         """tokens[B, T] continue every sequence at position `start`; returns logits [B, vocab] of the
@@ -249,6 +258,7 @@ class ShardedDecoder:
         B, T = tokens.shape
         M = B * T
         end = start + T
+        self.check_capacity(B, end)
         pos0 = torch.tensor([start], dtype=torch.long, device=self.dev)
         x = self.embed[tokens.reshape(-1)]                                     # [M, d]
         scale = 1.0 / math.sqrt(D)
@@ -294,6 +304,8 @@ class GraphedDecoder:
         self.lens = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.logits = None
         self.graph = None
+        self.position = 0                # host mirror of `pos`: every step is checked against the cache before it is launched
+        model.check_capacity(batch, 0)
 
     @torch.no_grad()
     def _step(self):
@@ -318,12 +330,15 @@ class GraphedDecoder:
 
     def start(self, first_tokens: torch.Tensor, position: int):
         """Continue from `position` (the prompt length) with `first_tokens` [B] as the next input."""
+        self.m.check_capacity(self.B, position + 1)
         self.tokens.copy_(first_tokens.reshape(self.B, 1))
         self.pos.fill_(position)
         self.lens.fill_(position + 1)
+        self.position = position
 
     def capture(self):
         """Run one eager step (first-call set-up happens outside capture), rewind, then capture."""
+        self.m.check_capacity(self.B, self.position + 1)
         saved = (self.tokens.clone(), self.pos.clone(), self.lens.clone())
         pg = self.m._push_gather() if self.m.world > 1 else None
         before = pg.calls if pg is not None else 0
@@ -341,6 +356,8 @@ class GraphedDecoder:
 
     def step(self):
         """Advance every sequence by one token; returns the (static) logits tensor of this step."""
+        self.m.check_capacity(self.B, self.position + 1)
+        self.position += 1
         if self.graph is None:
             self.logits = self._step()
         else:
@@ -359,4 +376,7 @@ def greedy_generate(model: ShardedDecoder, prompts: torch.Tensor, steps: int):
         out.append(nxt)
         if s + 1 < steps:
             logits = model.forward(nxt[:, None], P + s)
+    if model.dev.type == "cuda":
+        from .. import _lib
+        _lib.check_device_status(model.dev)       # a bounded wait that ran out (a gather, a matmul) must not pass silently
     return torch.stack(out, 1), logits

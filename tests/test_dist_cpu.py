@@ -139,3 +139,29 @@ def test_peer_gather_buffer_rotation_never_reuses_a_live_buffer():
     import pytest
     with pytest.raises(RuntimeError):
         pick_cycle(421, 3, 0)                         # 1 mod 3, 4, 5 and 7: no modulus on offer works
+
+
+def test_cache_capacity_is_checked_on_the_host_before_any_launch():
+    """A prompt or a decode step that would run past the KV cache or the rotary tables raises on the host;
+    nothing reaches a kernel (the cache-append kernel takes its position from device memory)."""
+    import pytest
+    from mlx_batch_invariant_b200.runner import GraphedDecoder
+
+    m = _model(0, 1, None)                                         # max_batch 3, max_len 32
+    with pytest.raises(ValueError, match="max_len"):
+        m.forward(torch.zeros(2, 33, dtype=torch.long), 0)
+    with pytest.raises(ValueError, match="max_len"):
+        m.forward(torch.zeros(2, 4, dtype=torch.long), 30)
+    with pytest.raises(ValueError, match="max_batch"):
+        m.forward(torch.zeros(4, 2, dtype=torch.long), 0)
+    m.forward(torch.zeros(3, 32, dtype=torch.long), 0)              # exactly full is fine
+    gd = GraphedDecoder(m, 3)
+    with pytest.raises(ValueError, match="max_len"):
+        gd.start(torch.zeros(3, dtype=torch.long), 32)
+    gd.start(torch.zeros(3, dtype=torch.long), 30)
+    gd.step()
+    gd.step()                                                      # positions 30 and 31: the last two slots
+    with pytest.raises(ValueError, match="max_len"):
+        gd.step()
+    with pytest.raises(ValueError, match="max_batch"):
+        GraphedDecoder(m, 4)

@@ -100,3 +100,29 @@ def test_glue_kernels_match_framework_formulas(bi):
         got = KernelBackend().swiglu(gu).float()
         assert (ref - got).abs().max() <= 2e-2 * ref.abs().max()
         assert torch.equal(KernelBackend().swiglu(gu[2:3]), KernelBackend().swiglu(gu)[2:3])
+
+
+def test_cache_append_past_capacity_writes_nothing_and_reports(bi):
+    """The cache-append kernel reads its position from device memory; one past the cache must leave the cache
+    and q untouched and set the status word (no fault, no stray write)."""
+    from mlx_batch_invariant_b200 import _lib
+    from mlx_batch_invariant_b200.runner.decoder import KernelBackend
+
+    B, T, hq, hkv, D, cap = 2, 1, 4, 2, 64, 16
+    dt = torch.bfloat16
+    qkv = torch.randn(B * T, (hq + 2 * hkv) * D).to(dt).cuda()
+    cos = torch.ones(cap, D, device="cuda")
+    sin = torch.zeros(cap, D, device="cuda")
+    kc = torch.full((B, hkv, cap + 8, D), 7.0, dtype=dt, device="cuda")[:, :, :cap]     # a view: memory follows the cache
+    vc = torch.full((B, hkv, cap + 8, D), 7.0, dtype=dt, device="cuda")[:, :, :cap]
+    bi.check_device_status()
+    for bad in (cap, cap + 3):
+        KernelBackend().rope_append(qkv, cos, sin, torch.tensor([bad], dtype=torch.long, device="cuda"), B, T, hq, hkv, D, kc, vc)
+        torch.cuda.synchronize()
+        assert bool((kc._base == 7).all()) and bool((vc._base == 7).all())
+        with pytest.raises(_lib.KernelError):
+            bi.check_device_status()
+    KernelBackend().rope_append(qkv, cos, sin, torch.tensor([cap - 1], dtype=torch.long, device="cuda"), B, T, hq, hkv, D, kc, vc)
+    torch.cuda.synchronize()
+    assert bool((kc[:, :, cap - 1] != 7).any())
+    bi.check_device_status()

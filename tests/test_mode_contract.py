@@ -126,3 +126,41 @@ def test_direct_kernel_calls_reject_cpu_tensors_and_bad_shapes():
     with pytest.raises(AssertionError):
         q = torch.randn(1, 2, 3, 64)
         bi.batch_invariant_decode_attention(q, q, q, scale=1.0)
+
+
+def test_mlx_symbols_fall_back_to_the_mlx_stock_ops():
+    """With ``mlx.core`` importable the mode patches its six symbols too. Arrays that the kernels cannot take
+    (here: host memory) are counted and then handed to the *MLX* stock callable that was installed before --
+    never to a torch op, which could not take an mx.array -- and strict mode raises instead."""
+    from tests import _fake_mlx
+
+    mx, calls, uninstall = _fake_mlx.install()
+    try:
+        stock = (mx.matmul, mx.addmm, mx.quantized_matmul, mx.fast.rms_norm, mx.fast.scaled_dot_product_attention,
+                 mx.array.__matmul__)
+        a, b, c = mx.array(torch.randn(3, 8)), mx.array(torch.randn(8, 4)), mx.array(torch.randn(3, 4))
+        q = mx.array(torch.randn(1, 4, 1, 32))
+        kv = mx.array(torch.randn(1, 2, 9, 32))
+        bi.reset_stats()
+        with bi.set_batch_invariant_mode():
+            assert mx.matmul is not stock[0] and mx.array.__matmul__ is not stock[5]
+            out = mx.matmul(a, b)
+            assert isinstance(out, mx.array) and out.shape == (3, 4)
+            assert isinstance(a @ b, mx.array)
+            mx.addmm(c, a, b, alpha=2.0)
+            mx.quantized_matmul(a, mx.array(torch.zeros(4, 1, dtype=torch.int32)), mx.array(torch.ones(4, 1)),
+                                mx.array(torch.zeros(4, 1)), group_size=8, bits=4)
+            mx.fast.rms_norm(a, None, 1e-5)
+            mx.fast.scaled_dot_product_attention(q, kv, kv, scale=0.2)
+            with bi.set_batch_invariant_mode(strict=True):
+                with pytest.raises(RuntimeError, match="no kernel for matmul"):
+                    mx.matmul(a, b)
+        assert calls == ["matmul", "array.__matmul__", "addmm", "quantized_matmul", "rms_norm", "sdpa"]
+        fb = bi.stats()["fallbacks"]
+        assert fb["matmul:not-cuda"] == 3 and fb["addmm:not-cuda"] == 1 and fb["rms_norm:not-cuda"] == 1
+        assert fb["quantized_matmul:affine-4bit-g8-T"] == 1 and fb["sdpa:sinks-or-shape"] == 1
+        assert (mx.matmul, mx.addmm, mx.quantized_matmul, mx.fast.rms_norm, mx.fast.scaled_dot_product_attention,
+                mx.array.__matmul__) == stock
+    finally:
+        uninstall()
+        bi.reset_stats()
