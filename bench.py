@@ -5,9 +5,12 @@
 One "step" is one pass of the workload over one batch of seeded synthetic input.
 Prints ONE JSON line (rank 0). Workloads:
 
-    llama3_8b_decode   Llama-3-8B-architecture decoder, random init, bf16, batch 64, 512-token prompts:
-                       one step = one greedy decode step of all 64 sequences                -> tok/s (default)
-                       sharded column/head-parallel over --gpus N with all-gather (strong scaling)
+    llama3_8b_decode   Llama-3-8B-architecture decoder, random init, bf16, batch 64 (--batch 1/4/16/64), 512-token
+                       prompts: one step = one greedy decode step of all sequences          -> tok/s (default)
+                       sharded column/head-parallel over --gpus N with all-gather (strong scaling). The line
+                       also carries `row0_logits_hash` / `tokens_hash` (row 0 is the same probe prompt at every
+                       batch size and GPU count: the digests must not change) and, at one GPU, an `ops` block
+                       with the op-level components of the metric measured in the same run.
     llama3_8b_decode_q4  the same with 4-bit group-64 weights
     matmul_bf16_m256   dense y = x @ W^T, x[256,4096], W[4096,4096], bf16     -> TFLOP/s
     qmm4_decode        4-bit group-64 quantized matmul, M=1, K=4096 -> N=14336  -> GB/s
@@ -20,9 +23,11 @@ distinct buffers than fit in L2 so every step streams from HBM, max over ranks. 
 inputs resident in HBM; `e2e` goes through the public API from pinned host buffers and back.
 With --gpus N > 1 the op-level workloads run as N independent replicas (no collective: the
 op itself does not shard), value = sum over ranks / max time; the decoder workloads shard the
-model (every linear by weight rows, attention by KV head) and join slices by NCCL all-gather.
+model (every linear by weight rows, attention by KV head) and join slices by all-gather (the library's
+peer-memory gather, or NCCL: `config.collective` says which ran).
 --impl reference times the CPU restatement of the reference algorithm (the oracle; the
-reference itself is Metal-only and cannot run here) on the host cores.
+reference itself is Metal-only and cannot run here) on the host cores: for the decoder, every step is
+one whole decode step of one sequence (all layers, attention, lm_head).
 """
 
 from __future__ import annotations
@@ -133,7 +138,7 @@ class MatmulBF16(Workload):
         self.x_host = torch.randn(self.M, self.K, generator=g).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(dev)
         self.y_host = torch.empty(self.M, self.N, dtype=torch.bfloat16).pin_memory()
-        self.launches_per_step = 2                        # split kernel + combine (AUTO splits up to M = 256 here)
+        self.launches_per_step = 1                        # M = 256 folds in place (64-row batch tiles)
 
     def step(self, i):
         return self.bi.batch_invariant_matmul(self.x, self.W[i % self.nbuf].T)
@@ -180,11 +185,11 @@ class QMM4Decode(Workload):
     M, N, K, gs, bits = 1, 14336, 4096, 64, 4
 
     def __init__(self, torch, bi, dev):
-        from oracle.reference import quantize_affine
+        from mlx_batch_invariant_b200.runner.decoder import quantize_rows
         self.torch, self.bi, self.dev = torch, bi, dev
         g = torch.Generator().manual_seed(0)
-        W = torch.randn(self.N, self.K, generator=g) * 0.02
-        p, s, b = quantize_affine(W, group_size=self.gs, bits=self.bits, dtype=torch.bfloat16)
+        W = (torch.randn(self.N, self.K, generator=g) * 0.02).to(torch.bfloat16)
+        p, s, b = quantize_rows(W.to(dev), self.gs, self.bits)
         wbytes = p.numel() * 4
         self.nbuf = L2_BYTES * 2 // wbytes + 1
         self.p = [p.to(dev).clone() for _ in range(self.nbuf)]
@@ -433,7 +438,8 @@ def run_ours(args):
                     "peak_source": f"of {pk['which']}"}
         from oracle import reference as R
         cores = os.cpu_count() or 1
-        cv, sample = wl.cpu_sample(R, cores) if world == 1 or True else (None, "")
+        R.set_threads(cores)                                # a launcher may have pinned OMP_NUM_THREADS to 1
+        cv, sample = wl.cpu_sample(R, cores)
         line = {
             "metric": wl.metric, "value": round(wl.value(per) * world, 3), "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(per * 1e3, 5),
@@ -460,38 +466,103 @@ def run_ours(args):
 MODEL_B, MODEL_P = 64, 512
 
 
-def _model_bytes_per_step(cfg, quant, B, kv_tokens):
-    """Algorithmic bytes of one decode step: every linear weight once, the KV cache once."""
+def _model_bytes_per_step(cfg, quant, B, kv_tokens, world=1):
+    """Algorithmic bytes ONE GPU moves in a decode step: its shard of every sharded linear, the whole of the
+    replicated output projection, its KV heads' cache (the embedding rows read are negligible)."""
     D = cfg.head_dim
-    per_layer = (cfg.n_heads * D + 2 * cfg.n_kv_heads * D) * cfg.d_model + cfg.d_model * cfg.n_heads * D + 3 * cfg.ffn * cfg.d_model
-    params = cfg.n_layers * per_layer + cfg.vocab * cfg.d_model
-    wbytes = params * (2.0 if quant is None else (quant[0] / 8 + 4 / quant[1]))
+    wb = 2.0 if quant is None else (quant[0] / 8 + 4 / quant[1])
+    sharded = cfg.n_layers * ((cfg.n_heads * D + 2 * cfg.n_kv_heads * D) * cfg.d_model + 3 * cfg.ffn * cfg.d_model) + cfg.vocab * cfg.d_model
+    replicated = cfg.n_layers * cfg.d_model * cfg.n_heads * D if world > 1 else 0
+    if world == 1:
+        sharded += cfg.n_layers * cfg.d_model * cfg.n_heads * D
     kv = cfg.n_layers * 2 * cfg.n_kv_heads * D * 2 * kv_tokens * B
-    return wbytes + kv
+    return (sharded / world + replicated) * wb + kv / world
 
 
-def _cpu_tok_per_s(R, torch, cfg):
-    """Oracle port on a bounded sample: the four linears and RMSNorms of one layer plus the lm_head for
-    one token (CUDA-core order of the K-group algorithm), extrapolated to the 32 layers."""
+def _cpu_decode_token(R, torch, cfg, keys):
+    """One whole greedy decode step of ONE sequence through the oracle port: every layer's RMSNorms, four
+    linears (CUDA-core order of the K-group algorithm), the split-KV attention over `keys` cached keys, and the
+    lm_head. One layer's random weights are reused for all layers (the work is the same; 15 GB of distinct
+    weights would take longer to draw than to use). Returns seconds."""
     g = torch.Generator().manual_seed(0)
     dt = torch.bfloat16
-    D = cfg.head_dim
-    x = torch.randn(1, cfg.d_model, generator=g).to(dt)
-    shapes = [((cfg.n_heads + 2 * cfg.n_kv_heads) * D, cfg.d_model), (cfg.d_model, cfg.n_heads * D), (2 * cfg.ffn, cfg.d_model), (cfg.d_model, cfg.ffn)]
-    ws = [(torch.randn(n, k, generator=g) * 0.02).to(dt).T.contiguous() for n, k in shapes]
-    head = (torch.randn(cfg.vocab // 8, cfg.d_model, generator=g) * 0.02).to(dt).T.contiguous()
-    nw = torch.ones(cfg.d_model, dtype=dt)
+    D, d = cfg.head_dim, cfg.d_model
+    mk = lambda n, k: (torch.randn(n, k, generator=g) * cfg.init_std).to(dt).T.contiguous()
+    wqkv, wo = mk((cfg.n_heads + 2 * cfg.n_kv_heads) * D, d), mk(d, cfg.n_heads * D)
+    wgu, wdown, head = mk(2 * cfg.ffn, d), mk(d, cfg.ffn), mk(cfg.vocab, d)
+    nw = torch.ones(d, dtype=dt)
+    kc = torch.randn(1, cfg.n_kv_heads, keys, D, generator=g).to(dt)
+    vc = torch.randn(1, cfg.n_kv_heads, keys, D, generator=g).to(dt)
+    x = torch.randn(1, d, generator=g).to(dt)
     t0 = time.perf_counter()
-    for w in ws:
-        a = torch.randn(1, w.shape[0], generator=g).to(dt)
-        R.rms_norm(a, None, 1e-5)
-        R.matmul_f32order(a, w)
-    t_layer = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    R.matmul_f32order(x, head)
-    t_head = (time.perf_counter() - t0) * 8
-    del nw
-    return 1.0 / (cfg.n_layers * t_layer + t_head), f"1 of {cfg.n_layers} layers' linears and 1/8 of the lm_head for one token, extrapolated ({t_layer + t_head / 8:.1f} s of CPU work)"
+    for _ in range(cfg.n_layers):
+        h = R.rms_norm(x, nw, cfg.eps)
+        qkv = R.matmul_f32order(h, wqkv)
+        q = qkv[:, :cfg.n_heads * D].reshape(1, cfg.n_heads, 1, D)
+        a = R.attn_decode(q, kc, vc, scale=D ** -0.5)
+        x = x + R.matmul_f32order(a.reshape(1, cfg.n_heads * D), wo)
+        h = R.rms_norm(x, nw, cfg.eps)
+        gu = R.matmul_f32order(h, wgu).float()
+        act = (torch.nn.functional.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]).to(dt)
+        x = x + R.matmul_f32order(act, wdown)
+    logits = R.matmul_f32order(R.rms_norm(x, nw, cfg.eps), head)
+    int(logits.float().argmax())
+    return time.perf_counter() - t0
+
+
+def _cpu_tok_per_s(R, torch, cfg, keys=560):
+    sec = _cpu_decode_token(R, torch, cfg, keys)
+    return 1.0 / sec, (f"one whole decode step of 1 of the {MODEL_B} sequences ({cfg.n_layers} layers: norms, four linears, "
+                       f"{keys}-key attention; lm_head), {sec:.1f} s of CPU work")
+
+
+def _hash8(t):
+    """blake2b-8 of a tensor's raw bits (the reference's harness/dump_bits.py:32-40 digest)."""
+    import hashlib
+    import torch
+    raw = t.detach().contiguous().cpu()
+    raw = raw.view(torch.int16) if raw.element_size() == 2 else (raw.view(torch.int32) if raw.element_size() == 4 else raw)
+    return hashlib.blake2b(raw.numpy().tobytes(), digest_size=8).hexdigest()
+
+
+def _model_prompts(torch, cfg, B, P):
+    """Row 0 is the probe prompt (seed 0, the same for every batch size and GPU count); the other rows are
+    fillers reseeded per (B, row), as the reference's model sweep builds its batches (harness/model_sweep.py:100-108)."""
+    rows = [torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(0))]
+    for r in range(1, B):
+        rows.append(torch.randint(0, cfg.vocab, (P,), generator=torch.Generator().manual_seed(1000 + 7 * B + r)))
+    return torch.stack(rows, 0)
+
+
+def _ops_block(torch, bi, dev, pk, steps=20):
+    """The op-level components of the headline metric, measured in this same run (each a CUDA-graph replay of
+    `steps` calls over rotated buffers): dense bf16 M=256 TFLOP/s beside cuBLAS, 4-bit decode GB/s, decode
+    attention GB/s, each with its fraction of the measured peak."""
+    out = {}
+    def timed(wl, fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fn(i)
+        g.replay()
+        return timed_region(torch, lambda i: g.replay(), 1, lambda: None) / steps
+    for cls in (MatmulBF16, QMM4Decode, AttnDecode):
+        wl = cls(torch, bi, dev)
+        per = timed(wl, wl.step)
+        ent = {"value": round(wl.value(per), 1), "unit": wl.unit, "us": round(per * 1e6, 2)}
+        if cls is MatmulBF16:
+            lib_per = timed(wl, lambda i: torch.matmul(wl.x, wl.W[i % wl.nbuf].T))
+            ent.update(frac=round(wl.value(per) / pk["bf16_tflops"], 4), frac_of="measured bf16 burst",
+                       cublas_us=round(lib_per * 1e6, 2), vs_cublas=round(lib_per / per, 3))
+        else:
+            ent.update(frac=round(wl.value(per) / pk["hbm_gbs"], 4), frac_of="measured HBM copy")
+        out[wl.name] = ent
+        del wl
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_model(args, quant):
@@ -514,26 +585,42 @@ def run_model(args, quant):
     from mlx_batch_invariant_b200.runner import LLAMA3_8B, GraphedDecoder, ShardedDecoder
     _lib.load()
     cfg = LLAMA3_8B
-    B, P = MODEL_B, MODEL_P
+    B, P = args.batch, MODEL_P
     warm = max(args.warmup, 3)
+    pk = peaks()
+    # op-level components of the headline metric, in the same run (single GPU only: the ops do not shard)
+    ops_block = _ops_block(torch, bi, dev, pk) if (world == 1 and not args.no_ops) else None
     total_steps = warm + args.steps * 2 + 8
     model = ShardedDecoder(cfg, rank=rank, world=world, device=dev, quant=quant, max_batch=B, max_len=P + total_steps + 1)
-    g = torch.Generator().manual_seed(0)
-    prompts = torch.randint(0, cfg.vocab, (B, P), generator=g).to(dev)
+    prompts = _model_prompts(torch, cfg, B, P).to(dev)
     logits = model.forward(prompts, 0)
+    # Bit evidence: row 0 is the same probe prompt at every batch size and GPU count, so these digests must be
+    # the same in every run of this workload (prefill logits, then the logits and tokens of decode steps 1-3).
+    row0_bits = [logits[0].clone()]
+    row0_tokens = [logits[0].argmax().reshape(1).clone()]
     gd = GraphedDecoder(model, B)
     gd.start(logits.argmax(-1), P)
+    lib = _lib.load()
     graphed = True
+    c0 = lib.bi_launch_count()
     try:
         gd.capture()
+        launches_per_step = (lib.bi_launch_count() - c0) // 2          # capture() runs the step twice: eagerly, then recorded
     except Exception as e:                                  # a step that cannot be captured still runs eagerly
         graphed = False
         gd.graph = None
         gd.start(logits.argmax(-1), P)
+        launches_per_step = None
         if rank == 0:
             print(f"bench.py: CUDA-graph capture failed ({type(e).__name__}: {e}); timing eager steps", file=sys.stderr)
-    for _ in range(warm):
-        gd.step()
+    for i in range(warm):
+        c1 = lib.bi_launch_count()
+        lg = gd.step()
+        if launches_per_step is None:
+            launches_per_step = lib.bi_launch_count() - c1
+        if i < 3:
+            row0_bits.append(lg[0].clone())
+            row0_tokens.append(gd.tokens[0].reshape(1).clone())
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -559,13 +646,16 @@ def run_model(args, quant):
         sec, sec_e2e = float(t[0]), float(t[1])
     per, per_e2e = sec / args.steps, sec_e2e / args.steps
     if rank == 0:
-        pk = peaks()
         kv_tokens = P + warm + args.steps // 2
-        bytes_step = _model_bytes_per_step(cfg, quant, B, kv_tokens) / world      # per GPU
+        bytes_step = _model_bytes_per_step(cfg, quant, B, kv_tokens, world)       # per GPU
         achieved = bytes_step / per / 1e9
-        launches = (cfg.n_layers * (4 * 2 + 2 + 2) + 3)                           # matmul(+combine) x4, rmsnorm x2, attention x2 per layer; head
+        gather = "none (single GPU)"
+        if world > 1:
+            gather = ("peer-memory push all-gather (bi_push_gather), 97 per step" if model._pg is not None
+                      else "NCCL all_gather_into_tensor, 97 per step")
         from oracle import reference as R
         cores = os.cpu_count() or 1
+        R.set_threads(cores)                                # torchrun pins OMP_NUM_THREADS to 1; the baseline uses every core
         cv, sample = _cpu_tok_per_s(R, torch, cfg)
         name = "llama3_8b_decode" + ("" if quant is None else "_q4")
         line = {
@@ -575,18 +665,28 @@ def run_model(args, quant):
             "data": "synthetic",
             "config": {"workload": name, "architecture": "Llama-3-8B (32 layers, d 4096, 32/8 heads, head_dim 128, ffn 14336, vocab 128256), random init",
                        "global_batch": B, "prompt_len": P, "decode": "greedy, KV cache, CUDA graph replay" if graphed else "greedy, KV cache, eager",
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: weight-row / KV-head shards, NCCL all-gather",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world}: weight-row / KV-head shards, output projection replicated",
+                       "collective": gather,
                        "l2": "15 GB of weights streamed per step (>> L2)"},
             "clocks": clocks,
             "e2e": {"value": round(B / per_e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
                     "ms_per_step": round(per_e2e * 1e3, 4)},
-            "gpu_launches": launches * args.steps,
+            "gpu_launches": int(launches_per_step or 0) * args.steps,
+            "gpu_launches_per_step": int(launches_per_step or 0),
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": f"of {pk['which']}",
-                         "kernel": "whole decode step per GPU: weights + KV cache bytes / step time"},
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None,
+                         "traffic_note": "no whole-step capture (a step is ~300 launches; ncu captures are kept to one kernel): "
+                                         "per-kernel DRAM traffic is in profiles/ and in the op workloads' lines",
+                         "peak_source": f"of {pk['which']}",
+                         "kernel": "whole decode step per GPU: its weight shards + replicated output projection + its KV heads' cache, / step time"},
             "cpu_baseline": {"value": round(cv, 4), "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
             "fallbacks": fallbacks,
+            "row0_logits_hash": _hash8(torch.stack(row0_bits, 0)),
+            "tokens_hash": _hash8(torch.cat(row0_tokens, 0)),
+            "hash_of": "row 0 (the probe prompt): logits of the prefill and of decode steps 1-3; its first 4 greedy tokens",
         }
+        if ops_block is not None:
+            line["ops"] = ops_block
         print(json.dumps(line), flush=True)
     _shutdown(torch, dist, [gd])
 
@@ -620,19 +720,22 @@ def run_reference(args):
     class _NoDev:                                          # build the workload's host-side inputs only
         pass
     # CPU-only construction of the same seeded inputs
+    R.set_threads(cores)
     if args.workload.startswith("llama3_8b_decode"):
         from mlx_batch_invariant_b200.runner import LLAMA3_8B
         vals = []
         sample = ""
         for i in range(args.warmup + args.steps):
-            v, sample = _cpu_tok_per_s(R, torch, LLAMA3_8B)
+            v, sample = _cpu_tok_per_s(R, torch, LLAMA3_8B)             # every step really runs one whole token
             if i >= args.warmup:
                 vals.append(v)
         v = statistics.mean(vals)
         line = {"impl": "reference", "metric": "model tok/s", "value": round(v, 4), "unit": "tok/s",
                 "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 / v, 1),
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": args.workload, "global_batch": MODEL_B, "prompt_len": MODEL_P},
+                "config": {"workload": args.workload, "global_batch": MODEL_B, "prompt_len": MODEL_P,
+                           "note": "the reference is Metal-only; this arm is its algorithm restated in C (oracle port) on the host cores, "
+                                   "one sequence per step (a bounded sample of the 64-sequence step)"},
                 "cpu_baseline": {"value": round(v, 4), "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
                 "e2e": {"value": round(v, 4), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
@@ -673,6 +776,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--workload", default="llama3_8b_decode", choices=["llama3_8b_decode", "llama3_8b_decode_q4"] + list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=MODEL_B, choices=[1, 4, 16, 64], help="decoder workloads: sequences per step")
+    ap.add_argument("--no-ops", action="store_true", help="decoder workloads: skip the op-level block of the line")
     args = ap.parse_args()
     model = args.workload.startswith("llama3_8b_decode")
     if args.steps is None:

@@ -45,6 +45,11 @@ int bi_version(void);
 /* Message for the last non-zero status returned on this thread ("" if none). */
 const char* bi_last_error(void);
 
+/* Kernels this library has launched in this process so far (every launch of every entry point, counted on
+ * the host when it is issued; a launch recorded into a CUDA graph counts once, when it is captured).
+ * No counterpart in the reference; benchmarks use it to state how many of the library's kernels a step runs. */
+unsigned long long bi_launch_count(void);
+
 /*
  * Device status word. The tensor-core matmul kernels wait on shared-memory
  * barriers with an iteration limit; a wait that runs out stores a non-zero

@@ -33,6 +33,7 @@ DTYPE_CODE = {torch.float32: BI_F32, torch.float16: BI_F16, torch.bfloat16: BI_B
 SIGNATURES = {
     "bi_version": (c_int, []),
     "bi_last_error": (c_char_p, []),
+    "bi_launch_count": (ctypes.c_ulonglong, []),
     "bi_read_device_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "bi_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_matmul_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int]),

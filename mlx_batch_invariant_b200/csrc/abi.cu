@@ -1,12 +1,16 @@
 // Library-wide entry points: version, the thread-local error message, and the
 // device status word helper.
 #include "bi_common.cuh"
+#include <atomic>
 #include <cstring>
 
 namespace bi {
 namespace {
 thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -20,6 +24,8 @@ int fail(int code, const char* fmt, ...) {
 extern "C" int bi_version(void) { return 100; /* 0.1.0 */ }
 
 extern "C" const char* bi_last_error(void) { return bi::g_err; }
+
+extern "C" unsigned long long bi_launch_count(void) { return bi::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int bi_read_device_status(const int32_t* status, int32_t* host_value, void* stream) {
     using namespace bi;

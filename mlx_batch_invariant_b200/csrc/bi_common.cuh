@@ -13,7 +13,11 @@ namespace bi {
 // Defined in abi.cu. Records `msg` for bi_last_error() and returns `code`.
 int fail(int code, const char* fmt, ...);
 
+// Defined in abi.cu: counts kernel launches of the library (read back by bi_launch_count()).
+void count_launch();
+
 inline int check_launch(const char* what) {
+    count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(BI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     return BI_OK;

@@ -256,3 +256,12 @@ void orc_dequant(const uint32_t* w, const void* scales, const void* biases, void
 /* round-trip helpers for the Python side */
 void orc_round_array(const float* x, void* y, int64_t n, int dt) { for (int64_t i = 0; i < n; ++i) store_el(y, i, dt, x[i]); }
 void orc_up_array(const void* x, float* y, int64_t n, int dt) { for (int64_t i = 0; i < n; ++i) y[i] = load_el(x, i, dt); }
+
+/* Worker threads of the OpenMP loops above (a launcher may have pinned OMP_NUM_THREADS to 1 in the environment;
+ * the timed CPU baseline wants every host core). The thread count never changes a bit of any result. */
+#ifdef _OPENMP
+#include <omp.h>
+int orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); return omp_get_max_threads(); }
+#else
+int orc_set_threads(int n) { (void)n; return 1; }
+#endif

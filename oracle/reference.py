@@ -39,8 +39,15 @@ def lib() -> ctypes.CDLL:
                                           c_int64, c_int64, c_int]
         L.orc_combine.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int]
         L.orc_dequant.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int]
+        L.orc_set_threads.restype = c_int
+        L.orc_set_threads.argtypes = [c_int]
         _lib = L
     return _lib
+
+
+def set_threads(n: int) -> int:
+    """Use n OpenMP threads in the oracle's loops (returns the count in effect)."""
+    return int(lib().orc_set_threads(int(n)))
 
 
 def _c(t: torch.Tensor) -> torch.Tensor:
