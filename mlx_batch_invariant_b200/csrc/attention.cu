@@ -28,6 +28,7 @@
 // decode_kernel and prefill_kernel call the same key_update() and merge
 // functions (merge_coeffs / merge_acc for the split fold), which is why a token's bits do not depend on which of the two
 // produced it.
+#include <algorithm>
 #include "bi_common.cuh"
 #include "bi_ptx.cuh"
 
@@ -592,6 +593,222 @@ __global__ void __launch_bounds__(32 * MAXW) decode_warp_stream_kernel(
     }
 }
 
+// ---- decode, a key per lane: for 16-bit K/V with head_dim 128, the layout the hardware likes best.
+// The canonical arithmetic is unchanged; what changes is who computes it:
+//   * scores: lane j of the warp owns key j of a 32-key block and evaluates the whole dot product of that key
+//     with each of the NH query heads that share the kv head -- the 32 virtual-lane fma chains and the xor tree
+//     16, 8, 4, 2, 1 become local packed-pair arithmetic (virtual lanes 2i and 2i+1 ride in one f32x2), so
+//     no shuffle is needed, each K element is converted once for all heads, and 32 keys proceed at once;
+//   * softmax scalars: the running maximum before each key is a prefix maximum over lanes (max is exact, so a
+//     parallel scan gives the bits of the sequential one), after which every lane computes its own key's
+//     exp(-|s - m|) -- 32 exponentials per instruction instead of one;
+//   * accumulation: lane d owns dims 4d..4d+3 of all NH heads and walks the block's keys in order:
+//     l = fma(l, corr, p), acc = fma(acc, corr, p * v), the factors read back from shared memory.
+// A warp is one work item (batch, kv head, chunk of NH heads, split) at a time; items are dealt to a
+// persistent grid round-robin, full splits first.
+// Launch-shape constants, from measurements on B200 (bf16, 32/8 heads): seven warps with two K blocks each beat
+// eight or ten warps with one (ten warps cap the kernel at 168 registers: 65 us against 50 us at 64 x 560 keys).
+constexpr int KL_WARPS = 7;    // warps per CTA (one CTA per SM)
+constexpr int KL_KBUFS = 2;    // K blocks in shared memory per warp: the next block is fetched a whole block ahead
+constexpr int KL_UNROLL = 8;   // keys of the accumulation loop in flight
+constexpr int KL_KEYS = 32;
+struct KLCfg {
+    static constexpr int ROWB = 256;                       // bytes of a K or V row (128 x 16 bit)
+    static constexpr int KPITCH = ROWB + 16;               // lanes read different rows at one column: no bank conflict
+    static constexpr int KBUF = KL_KEYS * KPITCH;
+    static constexpr int VBUF = KL_KEYS * ROWB;
+    static constexpr int QBYTES = 4 * 128 * 4;             // scaled queries of up to four heads, as packed pairs
+    static constexpr int CPBYTES = KL_KEYS * 4 * 16;       // (corr, corr, p, p) per key and head
+    static constexpr int WARP_BYTES = KL_KBUFS * KBUF + VBUF + QBYTES + CPBYTES;
+    static constexpr int SMEM_BYTES = KL_WARPS * WARP_BYTES;
+};
+
+// P_I for every head: the packed partial sums (part_{2I}, part_{2I+1}) of virtual lanes 2I and 2I+1 -- piece I of
+// the key's row (dims 8I .. 8I+7) against the queries' same dims, each a four-step fma chain from zero.
+template <typename T, int NH, int I>
+__device__ __forceinline__ void kl_leaf(const uint8_t* krow, const uint8_t* qs, uint64_t (&out)[NH]) {
+    const uint4 kw = *reinterpret_cast<const uint4*>(krow + 16 * I);
+    uint64_t k2[4];
+    k2[0] = ptx::pack2(word_lo<T>(kw.x), word_lo<T>(kw.z));   // (x0, x4)
+    k2[1] = ptx::pack2(word_hi<T>(kw.x), word_hi<T>(kw.z));   // (x1, x5)
+    k2[2] = ptx::pack2(word_lo<T>(kw.y), word_lo<T>(kw.w));   // (x2, x6)
+    k2[3] = ptx::pack2(word_hi<T>(kw.y), word_hi<T>(kw.w));   // (x3, x7)
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        const ulonglong2 qa = *reinterpret_cast<const ulonglong2*>(qs + h * 512 + I * 32);
+        const ulonglong2 qb = *reinterpret_cast<const ulonglong2*>(qs + h * 512 + I * 32 + 16);
+        uint64_t p = ptx::fma2_rn(qa.x, k2[0], ptx::pack2(0.0f, 0.0f));
+        p = ptx::fma2_rn(qa.y, k2[1], p);
+        p = ptx::fma2_rn(qb.x, k2[2], p);
+        p = ptx::fma2_rn(qb.y, k2[3], p);
+        out[h] = p;
+    }
+}
+// The xor tree over pieces: stride 8 is tree level 16 (virtual lanes v and v+16 are pieces I and I+8), then 4, 2, 1.
+template <typename T, int NH, int STRIDE, int I>
+__device__ __forceinline__ void kl_node(const uint8_t* krow, const uint8_t* qs, uint64_t (&out)[NH]) {
+    uint64_t a[NH], b[NH];
+    if constexpr (STRIDE == 8) {
+        kl_leaf<T, NH, I>(krow, qs, a);
+        kl_leaf<T, NH, I + 8>(krow, qs, b);
+    } else {
+        kl_node<T, NH, STRIDE * 2, I>(krow, qs, a);
+        kl_node<T, NH, STRIDE * 2, I + STRIDE>(krow, qs, b);
+    }
+#pragma unroll
+    for (int h = 0; h < NH; ++h) out[h] = ptx::add2_rn(a[h], b[h]);
+}
+
+template <typename T, int NH>
+__global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
+    float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
+    KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    using C = KLCfg;
+    constexpr int D = 128;
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* base = dec_smem + wid * C::WARP_BYTES;
+    uint8_t* kbuf = base;
+    uint8_t* vbuf = base + KL_KBUFS * C::KBUF;
+    uint8_t* qs = vbuf + C::VBUF;
+    uint8_t* cps = qs + C::QBYTES;
+    const uint32_t kbuf_s = (uint32_t)__cvta_generic_to_shared(kbuf), vbuf_s = (uint32_t)__cvta_generic_to_shared(vbuf);
+    const int G = Hq / Hkv;
+    const long long per_split = (long long)B * Hkv * nchunk;
+    const long long items = per_split * nsplit;
+
+    for (long long item = (long long)blockIdx.x * KL_WARPS + wid; item < items; item += (long long)gridDim.x * KL_WARPS) {
+        const int sp = (int)(item / per_split);
+        long long u = item - (long long)sp * per_split;
+        const int chunk = (int)(u % nchunk); u /= nchunk;
+        const int hk = (int)(u % Hkv);
+        const int b = (int)(u / Hkv);
+        const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+        const int j0 = sp * split;
+        const int nk = j0 < Lb ? (min(Lb, j0 + split) - j0) : 0;             // warp-uniform
+        if (nk == 0) continue;
+        const int h0 = hk * G + chunk * NH;
+        const int gcount = min(NH, G - chunk * NH);
+        const T* const kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+        const T* const vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
+        const int nblk = (nk + KL_KEYS - 1) / KL_KEYS;
+
+        // a block of 32 rows: 512 pieces of 16 bytes, 16 per lane, consecutive lanes on consecutive pieces
+        // lane's first piece of a block: row (lane >> 4), segment (lane & 15); each further piece is two rows on
+        const int64_t row_bytes = lay.sl * (int64_t)sizeof(T);
+        auto issue_rows = [&](const T* src, uint32_t dst, int pitch, int blk) {
+            const int r0 = blk * KL_KEYS + (lane >> 4);
+            const uint32_t d0 = dst + (lane >> 4) * pitch + (lane & 15) * 16;
+            if (blk * KL_KEYS + KL_KEYS <= nk) {
+                const uint8_t* g = reinterpret_cast<const uint8_t*>(src) + r0 * row_bytes + (lane & 15) * 16;
+#pragma unroll
+                for (int it = 0; it < 16; ++it)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + it * 2 * pitch), "l"(g + it * 2 * row_bytes) : "memory");
+            } else {
+#pragma unroll
+                for (int it = 0; it < 16; ++it) {
+                    const int64_t row = min(r0 + it * 2, nk - 1);                                 // past the end: re-read a valid row
+                    const uint8_t* g = reinterpret_cast<const uint8_t*>(src) + row * row_bytes + (lane & 15) * 16;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + it * 2 * pitch), "l"(g) : "memory");
+                }
+            }
+        };
+        __syncwarp();                                                        // the previous item's reads are done
+        issue_rows(kb, kbuf_s, C::KPITCH, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // scaled queries as packed pairs: pair (8i + d, 8i + 4 + d) at qs[h][i][d]
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            const T* qr = q + ((int64_t)b * Hq + h0 + min(h, gcount - 1)) * D;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int d = t * 32 + lane;
+                const int i = d >> 3, w = d & 7;
+                *reinterpret_cast<float*>(qs + h * 512 + i * 32 + (w & 3) * 8 + (w >> 2) * 4) = mul_rn(Cvt<T>::up(qr[d]), scale);
+            }
+        }
+        float m[NH], l[NH];
+        uint64_t acc[NH][2];
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            m[h] = -INFINITY; l[h] = 0.0f;
+            acc[h][0] = ptx::pack2(0.0f, 0.0f); acc[h][1] = ptx::pack2(0.0f, 0.0f);
+        }
+        for (int blk = 0; blk < nblk; ++blk) {
+            issue_rows(vb, vbuf_s, C::ROWB, blk);                            // lands while the scores are computed
+            if (KL_KBUFS == 2 && blk + 1 < nblk) issue_rows(kb, kbuf_s + ((blk + 1) & 1) * C::KBUF, C::KPITCH, blk + 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");            // this block's K rows have landed
+            __syncwarp();
+            const int cnt = min(KL_KEYS, nk - blk * KL_KEYS);
+            const bool valid = lane < cnt;
+            // ---- scores of key `lane` for every head
+            uint64_t dd[NH];
+            kl_node<T, NH, 1, 0>(kbuf + (KL_KBUFS == 2 ? (blk & 1) * C::KBUF : 0) + lane * C::KPITCH, qs, dd);
+            // ---- softmax scalars of the block
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                float d0, d1;
+                ptx::unpack2(dd[h], d0, d1);
+                const float s = add_rn(d0, d1);
+                float x = valid ? s : -INFINITY;                              // inclusive prefix maximum over the lanes
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const float y = __shfl_up_sync(0xffffffffu, x, off);
+                    if (lane >= off) x = fmaxf(x, y);
+                }
+                float before = __shfl_up_sync(0xffffffffu, x, 1);
+                before = fmaxf(m[h], lane == 0 ? -INFINITY : before);         // running maximum before this key
+                const float e = expf_canon(-fabsf(sub_rn(s, before)));
+                const bool rises = s >= before;
+                const float corr = rises ? e : 1.0f, p = rises ? 1.0f : e;
+                *reinterpret_cast<float4*>(cps + (lane * NH + h) * 16) = make_float4(corr, corr, p, p);
+                m[h] = fmaxf(m[h], __shfl_sync(0xffffffffu, x, 31));
+            }
+            if (KL_KBUFS == 2) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");        // V rows (and the next K rows) have landed
+            } else {
+                __syncwarp();                                                // every lane has read its K row
+                if (blk + 1 < nblk) issue_rows(kb, kbuf_s, C::KPITCH, blk + 1);  // lands while this block is accumulated
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 1;" ::: "memory");        // this block's V rows have landed
+            }
+            __syncwarp();
+            // ---- accumulation, key by key; lane owns dims 4*lane .. 4*lane+3 of every head
+#pragma unroll KL_UNROLL
+            for (int j = 0; j < cnt; ++j) {
+                const uint2 vw = *reinterpret_cast<const uint2*>(vbuf + j * C::ROWB + lane * 8);
+                const uint64_t v01 = ptx::pack2(word_lo<T>(vw.x), word_hi<T>(vw.x));
+                const uint64_t v23 = ptx::pack2(word_lo<T>(vw.y), word_hi<T>(vw.y));
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    const ulonglong2 cp = *reinterpret_cast<const ulonglong2*>(cps + (j * NH + h) * 16);
+                    float c, c_, p, p_;
+                    ptx::unpack2(cp.x, c, c_);
+                    ptx::unpack2(cp.y, p, p_);
+                    l[h] = fma_rn(l[h], c, p);
+                    acc[h][0] = ptx::fma2_rn(acc[h][0], cp.x, ptx::mul2_rn(cp.y, v01));
+                    acc[h][1] = ptx::fma2_rn(acc[h][1], cp.x, ptx::mul2_rn(cp.y, v23));
+                }
+            }
+            __syncwarp();                                                    // before the buffers are refilled
+        }
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            if (h < gcount) {
+                const int64_t po = ((int64_t)b * Hq + h0 + h) * nsplit + sp;
+                if (lane == 0) { pm[po] = m[h]; pl[po] = l[h]; }
+                float a0, a1, a2, a3;
+                ptx::unpack2(acc[h][0], a0, a1);
+                ptx::unpack2(acc[h][1], a2, a3);
+                *reinterpret_cast<float4*>(pacc + po * D + lane * 4) = make_float4(a0, a1, a2, a3);
+            }
+        }
+    }
+}
+
+
 template <typename T>
 __global__ void __launch_bounds__(256) decode_combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                                                              const float* __restrict__ pacc,
@@ -800,6 +1017,39 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
         const int64_t per16 = 16 / (int64_t)sizeof(T);
         const bool rows16 = aligned(k, 16) && aligned(v, 16) && lay.sb % per16 == 0 && lay.sh % per16 == 0 &&
                             lay.sl % per16 == 0 && (32 * DL * sizeof(T)) % 16 == 0;
+        if constexpr (DL == 4 && sizeof(T) == 2) {
+            // 16-bit K/V, head_dim 128: a key per lane (decode_keylane_kernel). Heads of a kv head share the warp in
+            // chunks of four (two, one); with few work items every head gets a warp of its own instead.
+            if (rows16 && (BH * nsplit) % 2 == 0) {
+                int nh = G >= 3 ? 4 : (G == 2 ? 2 : 1);
+                if (nh > 1 && B * Hkv * ((G + nh - 1) / nh) * nsplit < sms * 4) nh = 1;
+                const int nck = (G + nh - 1) / nh;
+                const int64_t items = B * Hkv * nck * nsplit;
+                const int64_t ctas = std::min<int64_t>(sms, (items + KL_WARPS - 1) / KL_WARPS);
+#define BI_KL_LAUNCH(NHV)                                                                                              \
+    do {                                                                                                                \
+        auto kern = decode_keylane_kernel<T, NHV>;                                                                      \
+        static bool attr_set[64] = {false};                                                                             \
+        int dev_ = 0;                                                                                                   \
+        cudaGetDevice(&dev_);                                                                                           \
+        if (dev_ < 0 || dev_ >= 64) dev_ = 0;                                                                           \
+        if (!attr_set[dev_]) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, KLCfg::SMEM_BYTES); \
+            if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
+            attr_set[dev_] = true;                                                                                      \
+        }                                                                                                               \
+        kern<<<(unsigned)ctas, 32 * KL_WARPS, KLCfg::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
+                                                                       (int)Hkv, (int)L, lay, scale, split, nsplit, nck); \
+    } while (0)
+                if (nh == 4) BI_KL_LAUNCH(4); else if (nh == 2) BI_KL_LAUNCH(2); else BI_KL_LAUNCH(1);
+#undef BI_KL_LAUNCH
+                int rck = check_launch("bi_attn_decode (key per lane)");
+                if (rck) return rck;
+                const int64_t n2k = BH * D;
+                decode_combine_kernel<T><<<(unsigned)((n2k + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
+                return check_launch("bi_attn_decode combine");
+            }
+        }
         const int nchunk4 = (G + 3) / 4;
         const int64_t streams = B * Hkv * nchunk4 * nsplit;
         if (rows16 && streams < sms * 24) {
