@@ -224,6 +224,12 @@ int bi_peer_close(void* ptr);
 int bi_push_gather(const void* local, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
                    int64_t row_bytes, int rank, int world, int32_t* status, void* stream);
 
+/* bi_push_gather with the SwiGLU gate computed on the way: gate_up is this rank's [rows, 2F] (gate columns, then
+ * up columns); the [rows, F] result of bi_swiglu on it is stored directly into every rank's gathered [rows, world*F]
+ * activation (same bits as bi_swiglu followed by bi_push_gather, one launch, no local copy). Same protocol state. */
+int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
+                          int64_t F, int dtype, int rank, int world, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

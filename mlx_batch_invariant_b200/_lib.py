@@ -58,6 +58,8 @@ SIGNATURES = {
     "bi_peer_close": (c_int, [c_void_p]),
     "bi_push_gather": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int64, c_int64,
                                c_int, c_int, c_void_p, c_void_p]),
+    "bi_push_gather_swiglu": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int64, c_int64,
+                                      c_int, c_int, c_int, c_void_p, c_void_p]),
     "bi_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int, c_void_p]),

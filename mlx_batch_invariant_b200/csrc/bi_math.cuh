@@ -48,6 +48,14 @@ __device__ __forceinline__ float expf_canon(float x) {
 __device__ __forceinline__ float rsqrt_canon(float v) { return __fdiv_rn(1.0f, __fsqrt_rn(v)); }
 __device__ __forceinline__ float div_canon(float a, float b) { return __fdiv_rn(a, b); }
 
+// silu(g) * u = (g * sigmoid(g)) * u with sigmoid from exp(-|g|): one exp, one divide, two multiplies.
+__device__ __forceinline__ float swiglu_canon(float g, float u) {
+    const float e = expf_canon(-fabsf(g));
+    const float den = add_rn(1.0f, e);
+    const float sig = g >= 0.0f ? div_canon(1.0f, den) : div_canon(e, den);
+    return mul_rn(mul_rn(g, sig), u);
+}
+
 // Storage-type conversions. Upcasts are exact; downcasts round to nearest even once.
 template <typename T> struct Cvt;
 template <> struct Cvt<float> {

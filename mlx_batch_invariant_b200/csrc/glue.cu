@@ -53,10 +53,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T
     const int64_t m = i / F, j = i - m * F;
     const float g = Cvt<T>::up(gu[m * 2 * F + j]);
     const float u = Cvt<T>::up(gu[m * 2 * F + F + j]);
-    const float e = expf_canon(-fabsf(g));
-    const float den = add_rn(1.0f, e);
-    const float sig = g >= 0.0f ? div_canon(1.0f, den) : div_canon(e, den);
-    out[i] = Cvt<T>::down(mul_rn(mul_rn(g, sig), u));
+    out[i] = Cvt<T>::down(swiglu_canon(g, u));
 }
 
 }  // namespace

@@ -41,18 +41,10 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
     return v;
 }
 
-// counters[0]: CTAs of the current launch that have pushed their part; counters[1]: epoch of the last gather.
-__global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restrict__ local, long long rows, int f16, int rank,
-                                                          int R, PeerPtrs dst, PeerPtrs flags, unsigned* counters,
-                                                          int32_t* status) {
-    const long long total = rows * f16;
-    const long long pitch = (long long)R * f16;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long m = i / f16;
-        const long long o = m * pitch + (long long)rank * f16 + (i - m * f16);
-        const uint4 v = local[i];
-        for (int r = 0; r < R; ++r) static_cast<uint4*>(dst.p[r])[o] = v;
-    }
+// After a CTA's stores: fence system-wide; the last CTA of the launch raises this rank's epoch flag at every peer and
+// waits (bounded) for theirs. counters[0]: CTAs of the current launch that have pushed their part; counters[1]: epoch
+// of the last gather.
+__device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& flags, unsigned* counters, int32_t* status) {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x != 0) return;
@@ -75,6 +67,49 @@ __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restric
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restrict__ local, long long rows, int f16, int rank,
+                                                          int R, PeerPtrs dst, PeerPtrs flags, unsigned* counters,
+                                                          int32_t* status) {
+    const long long total = rows * f16;
+    const long long pitch = (long long)R * f16;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / f16;
+        const long long o = m * pitch + (long long)rank * f16 + (i - m * f16);
+        const uint4 v = local[i];
+        for (int r = 0; r < R; ++r) static_cast<uint4*>(dst.p[r])[o] = v;
+    }
+    push_handshake(rank, R, flags, counters, status);
+}
+
+// The SwiGLU gate and the gather that follows it, in one kernel: this rank's slice out[m, j] = T(silu(gu[m, j]) *
+// gu[m, F + j]) (the arithmetic of bi_swiglu, element for element) is computed eight elements at a time and stored
+// straight into columns [rank * F, (rank + 1) * F) of every rank's gathered activation -- the local slice never
+// exists in memory, and the transfer overlaps the arithmetic piece by piece.
+template <typename T>
+__global__ void __launch_bounds__(256) push_gather_swiglu_kernel(const T* __restrict__ gu, long long rows, int F, int rank, int R,
+                                                                 PeerPtrs dst, PeerPtrs flags, unsigned* counters,
+                                                                 int32_t* status) {
+    constexpr int V = 16 / (int)sizeof(T);
+    const int f16 = F / V;
+    const long long total = rows * f16;
+    const long long pitch = (long long)R * f16;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / f16;
+        const int c = (int)(i - m * f16);
+        const uint4 gq = *reinterpret_cast<const uint4*>(gu + m * 2 * F + (long long)c * V);
+        const uint4 uq = *reinterpret_cast<const uint4*>(gu + m * 2 * F + F + (long long)c * V);
+        const T* gp = reinterpret_cast<const T*>(&gq);
+        const T* up = reinterpret_cast<const T*>(&uq);
+        uint4 oq;
+        T* op = reinterpret_cast<T*>(&oq);
+#pragma unroll
+        for (int e = 0; e < V; ++e) op[e] = Cvt<T>::down(swiglu_canon(Cvt<T>::up(gp[e]), Cvt<T>::up(up[e])));
+        const long long o = m * pitch + (long long)rank * f16 + c;
+        for (int r = 0; r < R; ++r) static_cast<uint4*>(dst.p[r])[o] = oq;
+    }
+    push_handshake(rank, R, flags, counters, status);
 }
 
 }  // namespace
@@ -149,4 +184,34 @@ extern "C" int bi_push_gather(const void* local, void* const* dst, void* const* 
     push_gather_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(local), rows, (int)f16, rank, world, d, f, counters, status);
     return check_launch("bi_push_gather");
+}
+
+extern "C" int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
+                                     int64_t F, int dtype, int rank, int world, int32_t* status, void* stream) {
+    using namespace bi;
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_push_gather_swiglu: dtype %d", dtype);
+    if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world)
+        return fail(BI_ERR_BAD_ARG, "bi_push_gather_swiglu: rank %d of %d (at most %d ranks)", rank, world, MAX_RANKS);
+    if (rows < 0 || F <= 0) return fail(BI_ERR_BAD_ARG, "bi_push_gather_swiglu: rows=%lld F=%lld", (long long)rows, (long long)F);
+    if (rows == 0) return BI_OK;
+    if (!gate_up || !dst || !flags || !counters) return fail(BI_ERR_BAD_ARG, "bi_push_gather_swiglu: null pointer");
+    const int64_t per = 16 / (int64_t)dtype_size(dtype);
+    if (F % per != 0 || !aligned(gate_up, 16) || F / per >= (1LL << 31))
+        return fail(BI_ERR_MISALIGNED, "bi_push_gather_swiglu: F must be a multiple of %lld elements and gate_up 16-byte aligned", (long long)per);
+    PeerPtrs d{}, f{};
+    for (int r = 0; r < world; ++r) {
+        if (!dst[r] || !flags[r]) return fail(BI_ERR_BAD_ARG, "bi_push_gather_swiglu: null peer pointer for rank %d", r);
+        if (!aligned(dst[r], 16)) return fail(BI_ERR_MISALIGNED, "bi_push_gather_swiglu: destination of rank %d is not 16-byte aligned", r);
+        d.p[r] = dst[r];
+        f.p[r] = flags[r];
+    }
+    const long long total = rows * (F / per);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 128) blocks = 128;
+    if (blocks < 1) blocks = 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define BI_PGS(TT) push_gather_swiglu_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(gate_up), rows, (int)F, rank, world, d, f, counters, status)
+    if (dtype == BI_F32) BI_PGS(float); else if (dtype == BI_F16) BI_PGS(__half); else BI_PGS(__nv_bfloat16);
+#undef BI_PGS
+    return check_launch("bi_push_gather_swiglu");
 }

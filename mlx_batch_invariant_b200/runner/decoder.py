@@ -228,6 +228,16 @@ class ShardedDecoder:
         dist.all_gather_into_tensor(buf, local, group=self.group)
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
+    def _gated(self, gu):
+        """SwiGLU of this rank's gate/up slice, gathered over the ranks: [M, 2F/R] -> [M, F]. With the peer
+        gather the gate is computed inside the gather kernel."""
+        if self.world > 1:
+            M, f2 = gu.shape
+            pg = self._push_gather()
+            if pg is not None and gu.is_contiguous() and pg.fits(M, (f2 // 2) * gu.element_size()):
+                return pg.gather_swiglu(gu)
+        return self._gather(self.ops.swiglu(gu))
+
     def _push_gather(self):
         """The peer-memory all-gather (CUDA ranks of one node). BI_GATHER=nccl keeps the library collective,
         BI_GATHER=push asks for the peer gather at any world size; unset, it is used at the world sizes it has
@@ -273,8 +283,7 @@ class ShardedDecoder:
                 a = self.ops.prefill_attention(q, kk, vv, scale)
             a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
             x, h = self.ops.add_rms_norm(x, self._lin(a, L["o"]), L["n2"], cfg.eps)
-            act = self.ops.swiglu(self._lin(h, L["gu"]))
-            delta = self._gather(self._lin(self._gather(act), L["down"]))
+            delta = self._gather(self._lin(self._gated(self._lin(h, L["gu"])), L["down"]))
             if li + 1 < len(self.layers):       # the add of this block and the first norm of the next, one launch
                 x, h = self.ops.add_rms_norm(x, delta, self.layers[li + 1]["n1"], cfg.eps)
             else:
@@ -318,8 +327,7 @@ class GraphedDecoder:
             a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
             x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"]), L["n2"], cfg.eps)
-            act = m.ops.swiglu(m._lin(h, L["gu"]))
-            delta = m._gather(m._lin(m._gather(act), L["down"]))
+            delta = m._gather(m._lin(m._gated(m._lin(h, L["gu"])), L["down"]))
             nxt = m.layers[li + 1]["n1"] if li + 1 < len(m.layers) else m.nf
             x, h = m.ops.add_rms_norm(x, delta, nxt, cfg.eps)
         logits = m._gather(m._lin(h, m.head))

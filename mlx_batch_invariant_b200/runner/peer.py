@@ -77,6 +77,26 @@ class PushGather:
         """A sequence of n gathers is about to be replayed back to back: pick the rotation modulus."""
         self.mod, self.calls = pick_cycle(n, self.mod, self.calls)
 
+    def _slot(self):
+        """Destination and flag pointer tables of the next gather, and its buffer index."""
+        b = self.calls % self.mod
+        self.calls += 1
+        arr = ctypes.c_void_p * self.world
+        return b, arr(*[base + b * self.cap for base in self.bases]), arr(*[base + NBUF * self.cap for base in self.bases])
+
+    def gather_swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
+        """gate_up[rows, 2F] of this rank -> swiglu of every rank's slice, [rows, world * F]: the gate is computed
+        while the slice is pushed (one launch; same bits as swiglu followed by gather)."""
+        rows, f2 = gate_up.shape
+        F = f2 // 2
+        b, dst, flags = self._slot()
+        status = _lib.status_word(self.dev)
+        _lib.check(self.lib.bi_push_gather_swiglu(gate_up.data_ptr(), dst, flags, self.counters.data_ptr(), rows, F,
+                                                  _lib.DTYPE_CODE[gate_up.dtype], self.rank, self.world, status.data_ptr(),
+                                                  _lib.stream_ptr(self.dev)))
+        n = rows * F * gate_up.element_size() * self.world
+        return self.own[b][:n].view(gate_up.dtype).view(rows, self.world * F)
+
     def gather(self, local: torch.Tensor) -> torch.Tensor:
         """local[rows, f] (contiguous) -> [rows, world * f], rank-major along the feature axis."""
         rows, f = local.shape
