@@ -208,6 +208,8 @@ int bi_add_rms_norm(const void* x, const void* delta, const void* w, void* sum_o
  *     r's destination buffer / flag array (uint32[world]) as mapped in THIS      *
  *     process (own buffers directly, the others through bi_peer_open).           *
  *   counters: uint32[2] in local device memory, zero before the first call.      *
+ *   wait: 1 = the kernel returns when every peer's slice has arrived; 0 = see     *
+ *   "Fused wait" below.                                                          *
  *   Every rank must issue the same sequence of gathers, and rotate over at        *
  *   least three destination buffers (a peer can be one gather ahead).            *
  * bi_peer_alloc / bi_peer_free: zero-filled device memory that a CUDA IPC        *
@@ -222,13 +224,34 @@ int bi_peer_export(void* ptr, uint8_t handle[64]);
 int bi_peer_open(const uint8_t handle[64], void** ptr);
 int bi_peer_close(void* ptr);
 int bi_push_gather(const void* local, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
-                   int64_t row_bytes, int rank, int world, int32_t* status, void* stream);
+                   int64_t row_bytes, int rank, int world, int wait, int32_t* status, void* stream);
 
 /* bi_push_gather with the SwiGLU gate computed on the way: gate_up is this rank's [rows, 2F] (gate columns, then
  * up columns); the [rows, F] result of bi_swiglu on it is stored directly into every rank's gathered [rows, world*F]
  * activation (same bits as bi_swiglu followed by bi_push_gather, one launch, no local copy). Same protocol state. */
 int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
-                          int64_t F, int dtype, int rank, int world, int32_t* status, void* stream);
+                          int64_t F, int dtype, int rank, int world, int wait, int32_t* status, void* stream);
+
+/* Fused wait. With wait = 0 a push gather stores its slice, raises this rank's flag at every peer and returns
+ * without waiting for theirs: the kernel that READS the gathered buffer waits instead, after it has started the
+ * part of its work that does not depend on the buffer. The *_awaiting entry points are bi_matmul / bi_qmm /
+ * bi_add_rms_norm with that wait in front of their first read of the activation (matmul: the weight tiles of the
+ * whole ring are already streaming while the kernel waits; add_rms_norm: `delta` is the gathered buffer).
+ *   flags: this rank's own flag array (the local one of the `flags` table given to the push);
+ *   epoch: &counters[1] of the push (device memory: the epoch of the gather just issued on the same stream).
+ * The wait is bounded (2 s); on expiry 0x20000 | peer << 8 | epoch lands in *status. flags == NULL: no wait.
+ * Same bits as the plain entry points. No counterpart in the reference (single device). */
+int bi_matmul_awaiting(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes,
+                       int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn,
+                       int dtype, int path, int32_t* status, void* stream, const uint32_t* flags,
+                       const uint32_t* epoch, int rank, int world);
+int bi_qmm_awaiting(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
+                    void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
+                    int group_size, int bits, int dtype, int path, int32_t* status, void* stream,
+                    const uint32_t* flags, const uint32_t* epoch, int rank, int world);
+int bi_add_rms_norm_awaiting(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows,
+                             int64_t D, float eps, int dtype, void* stream, const uint32_t* flags,
+                             const uint32_t* epoch, int rank, int world, int32_t* status);
 
 #ifdef __cplusplus
 }

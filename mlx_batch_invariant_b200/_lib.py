@@ -57,9 +57,15 @@ SIGNATURES = {
     "bi_peer_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_void_p)]),
     "bi_peer_close": (c_int, [c_void_p]),
     "bi_push_gather": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int64, c_int64,
-                               c_int, c_int, c_void_p, c_void_p]),
+                               c_int, c_int, c_int, c_void_p, c_void_p]),
     "bi_push_gather_swiglu": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int64, c_int64,
-                                      c_int, c_int, c_int, c_void_p, c_void_p]),
+                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bi_matmul_awaiting": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64, c_int64, c_int64,
+                                   c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "bi_qmm_awaiting": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64,
+                                c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "bi_add_rms_norm_awaiting": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "bi_add_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int, c_void_p]),

@@ -22,7 +22,7 @@ int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 // tiles 14.8 against 14.5 us). Below that the K groups are spread over CTAs (split) while the fp32 partials
 // stay L2-sized.
 TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
-    TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO};
+    TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO, Await{nullptr, nullptr, 0, 0}};
     const int64_t G = ngroups(K);
     const int64_t nt = (N + 127) / 128;
     const int64_t fill = (int64_t)sm_count() * 4 / 5;
@@ -119,10 +119,18 @@ extern "C" size_t bi_qmm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dt
     return bi_matmul_workspace_bytes(M, N, K, dtype);
 }
 
-extern "C" int bi_matmul(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
-                         int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
-                         int path, int32_t* status, void* stream) {
-    using namespace bi;
+namespace bi {
+namespace {
+int check_await(const char* op, const Await& aw) {
+    if (!aw.flags) return BI_OK;
+    if (!aw.epoch || aw.world < 1 || aw.world > 8 || aw.rank < 0 || aw.rank >= aw.world)
+        return fail(BI_ERR_BAD_ARG, "%s: bad gather to wait for (rank %d of %d)", op, aw.rank, aw.world);
+    return BI_OK;
+}
+
+int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
+                int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
+                int path, int32_t* status, void* stream, const Await& aw) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dtype %d", dtype);
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_matmul: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return BI_OK;
@@ -146,21 +154,43 @@ extern "C" int bi_matmul(const void* a, const void* b, void* out, void* workspac
         TcShape sh;
         rc = tc_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
         if (rc) return rc;
+        sh.await = aw;
         const int64_t w_ld = N == 1 ? K : b_sn;
         rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
         return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
     }
+    if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_awaiting: only weights on the tensor-core path can wait for a gather");
     bool split;
     rc = simt_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &split, &part);
     if (rc) return rc;
     return launch_simt_matmul(a, b, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, split, st);
 }
+}  // namespace
+}  // namespace bi
 
-extern "C" int bi_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
-                      void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
-                      int group_size, int bits, int dtype, int path, int32_t* status, void* stream) {
-    using namespace bi;
+extern "C" int bi_matmul(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
+                         int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
+                         int path, int32_t* status, void* stream) {
+    return bi::matmul_impl(a, b, out, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream,
+                           bi::Await{nullptr, nullptr, 0, 0});
+}
+
+extern "C" int bi_matmul_awaiting(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
+                                  int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
+                                  int path, int32_t* status, void* stream, const uint32_t* flags, const uint32_t* epoch,
+                                  int rank, int world) {
+    const bi::Await aw{flags, epoch, rank, world};
+    int rc = bi::check_await("bi_matmul_awaiting", aw);
+    if (rc) return rc;
+    return bi::matmul_impl(a, b, out, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream, aw);
+}
+
+namespace bi {
+namespace {
+int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
+             void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
+             int group_size, int bits, int dtype, int path, int32_t* status, void* stream, const Await& aw) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: dtype %d", dtype);
     if (bits != 4 && bits != 8) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: bits=%d (supported: 4, 8)", bits);
     if (group_size != 32 && group_size != 64 && group_size != 128)
@@ -187,12 +217,34 @@ extern "C" int bi_qmm(const void* x, const uint32_t* w, const void* scales, cons
         TcShape sh;
         rc = tc_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
         if (rc) return rc;
+        sh.await = aw;
         rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
         return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
     }
+    if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_awaiting: only weights on the tensor-core path can wait for a gather");
     bool split;
     rc = simt_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &split, &part);
     if (rc) return rc;
     return launch_simt_qmm(x, w, scales, biases, out, part, M, N, K, M == 1 ? K : x_sm, group_size, bits, dtype, split, st);
+}
+}  // namespace
+}  // namespace bi
+
+extern "C" int bi_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
+                      void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
+                      int group_size, int bits, int dtype, int path, int32_t* status, void* stream) {
+    return bi::qmm_impl(x, w, scales, biases, out, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
+                        stream, bi::Await{nullptr, nullptr, 0, 0});
+}
+
+extern "C" int bi_qmm_awaiting(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
+                               void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
+                               int group_size, int bits, int dtype, int path, int32_t* status, void* stream,
+                               const uint32_t* flags, const uint32_t* epoch, int rank, int world) {
+    const bi::Await aw{flags, epoch, rank, world};
+    int rc = bi::check_await("bi_qmm_awaiting", aw);
+    if (rc) return rc;
+    return bi::qmm_impl(x, w, scales, biases, out, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
+                        stream, aw);
 }

@@ -33,12 +33,21 @@ bool tc_matmul_supported(const void* x, int64_t x_ld, const void* w, int64_t w_l
 //   counters  split only: per-tile arrival counters (all zero) -> the last CTA of a tile folds the partials and
 //             writes `out` itself; nullptr -> the caller launches the combine kernel
 //   stage     quantized only: how the dequantized weight operand reaches the MMA
+//   await     the activation is the destination of a peer gather whose arrival nobody has waited for yet: the
+//             kernel starts streaming weights at once and reads the activation only after every peer's flag
+//             has reached *epoch (bounded wait); flags == nullptr -> nothing to wait for
+struct Await {
+    const uint32_t* flags;   // this rank's flag array, one word per rank
+    const uint32_t* epoch;   // the gather's epoch, in device memory
+    int rank, world;
+};
 struct TcShape {
     enum { STAGE_AUTO = 0, STAGE_SMEM = 1, STAGE_TMEM = 2 };
     bool split;
     int bm;
     unsigned* counters;
     int stage;
+    Await await;
 };
 int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, const TcQuant* q, void* out,
                      float* part, int64_t M, int64_t N, int64_t K, int dtype, const TcShape& shape, int32_t* status,

@@ -103,6 +103,7 @@ struct Params {
     const void* scales; // quantized only: [N, K/gs] in T
     const void* biases;
     int32_t* status;
+    Await await;        // activation produced by a peer gather that has not been waited for (flags == nullptr: none)
     unsigned* counters; // split path with in-kernel fold: one arrival counter per (weight tile, batch tile), zero between calls
     int M, N, K, G;
     int n_tiles, m_tiles;
@@ -396,15 +397,13 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             // path's partials out (measured faster also where several batch tiles re-read a weight tile).
             const uint64_t w_policy = ptx::l2_policy_evict_first();
             bool ok = true;
-            ChunkIter it(p, ub, ue);
-            for (; it.valid() && ok; it.next()) {
-                const int l = it.l;
-                if (it.ci >= LS && !wait_done(it.ci - LS, ROLE_TMA)) { ok = false; break; }
-                const int kc = it.ksteps();
+            // weight side of a chunk: arm the slot's barrier with all of the chunk's bytes, start the weight copies
+            auto issue_w = [&](const ChunkIter& c) {
+                const int l = c.l, kc = c.ksteps();
                 const uint32_t bar = bar_lfull(l);
                 const uint32_t tx = xb * (uint32_t)(p.box3d ? KS : kc) +
                                     (QBITS ? raw_box_bytes * (uint32_t)p.raw_boxes : wb * (uint32_t)(w3d ? KS : kc));
-                const int n0 = it.n0(), m0 = it.m0(), k0c = it.k0();
+                const int n0 = c.n0(), k0c = c.k0();
                 if (leader) {
                     ptx::mbar_expect_tx(bar, tx);
                     if (QBITS) {
@@ -414,15 +413,52 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                                   k0c * QBITS / 32 + b * (p.raw_span >> 2), n0, bar, w_policy);
                     }
                     if (w3d) ptx::tma_load_3d_hint(w_tile(l, 0), &tmap_w, 0, n0, k0c >> 6, bar, w_policy);
-                    if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, k0c >> 6, bar);
-                    if ((!QBITS && !w3d) || !p.box3d) {
-                        for (int j = 0; j < kc; ++j) {
-                            const int k0 = k0c + j * BLOCK_K;
-                            if (!QBITS && !w3d) ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0, n0, bar, w_policy);
-                            if (!p.box3d) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0, m0, bar);
-                        }
-                    }
+                    if (!QBITS && !w3d)
+                        for (int j = 0; j < kc; ++j) ptx::tma_load_2d_hint(w_tile(l, j), &tmap_w, k0c + j * BLOCK_K, n0, bar, w_policy);
                 }
+            };
+            // activation side of the same chunk
+            auto issue_x = [&](const ChunkIter& c) {
+                const int l = c.l, kc = c.ksteps();
+                const uint32_t bar = bar_lfull(l);
+                const int m0 = c.m0(), k0c = c.k0();
+                if (leader) {
+                    if (p.box3d) ptx::tma_load_3d(x_tile(l, 0), &tmap_x, 0, m0, k0c >> 6, bar);
+                    else
+                        for (int j = 0; j < kc; ++j) ptx::tma_load_2d(x_tile(l, j), &tmap_x, k0c + j * BLOCK_K, m0, bar);
+                }
+            };
+            ChunkIter it(p, ub, ue);
+            if (p.await.flags != nullptr && it.valid()) {
+                // The activation is still arriving from the other ranks. Fill the ring with weights first, then wait
+                // (bounded) for every peer's flag, then fetch the activation tiles of those chunks.
+                ChunkIter first(it);
+                int n = 0;
+                for (; it.valid() && n < LS; it.next(), ++n) issue_w(it);
+                const uint32_t epoch = *p.await.epoch;
+                const uint64_t t0 = ptx::globaltimer_ns();
+                for (int r = 0; r < p.await.world && ok; ++r) {
+                    if (r == p.await.rank) continue;
+                    uint32_t seen;
+                    do {
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.await.flags + r) : "memory");
+                        if ((int32_t)(seen - epoch) >= 0) break;
+                        if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                            *abort_flag = 1;
+                            if (p.status) atomicCAS(p.status, 0, (int)(0x20000 | (r << 8) | (epoch & 0xff)));
+                            ok = false;
+                            break;
+                        }
+                    } while (true);
+                }
+                asm volatile("fence.proxy.async.global;" ::: "memory");      // peers' stores, seen through the flags, before the TMA reads
+                for (int i = 0; i < n; ++i, first.next()) issue_x(first);   // also after a failed wait: the armed barriers must complete
+                __syncwarp();
+            }
+            for (; it.valid() && ok; it.next()) {
+                if (it.ci >= LS && !wait_done(it.ci - LS, ROLE_TMA)) { ok = false; break; }
+                issue_w(it);
+                issue_x(it);
                 __syncwarp();
             }
             if (!ok) {
@@ -1021,6 +1057,7 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     if (bm != 16 && bm != 32 && bm != 64 && bm != BLOCK_M) return fail(BI_ERR_BAD_ARG, "matmul: batch tile %d (16, 32, 64 or 128)", bm);
     Params p{};
     p.out = out; p.part = part; p.status = status;
+    p.await = shape.await;
     p.counters = split ? shape.counters : nullptr;
     p.scales = quant ? q->scales : nullptr; p.biases = quant ? q->biases : nullptr;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;

@@ -44,7 +44,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
 // After a CTA's stores: fence system-wide; the last CTA of the launch raises this rank's epoch flag at every peer and
 // waits (bounded) for theirs. counters[0]: CTAs of the current launch that have pushed their part; counters[1]: epoch
 // of the last gather.
-__device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& flags, unsigned* counters, int32_t* status) {
+// wait == 0: raise the flags and return; whoever reads the gathered buffer waits for the peers' flags itself.
+__device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& flags, unsigned* counters, int32_t* status, int wait) {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x != 0) return;
@@ -56,6 +57,7 @@ __device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& 
     __threadfence_system();
     for (int r = 0; r < R; ++r)
         if (r != rank) st_release_sys(static_cast<uint32_t*>(flags.p[r]) + rank, epoch);
+    if (!wait) return;
     const uint32_t* mine = static_cast<const uint32_t*>(flags.p[rank]);
     const uint64_t t0 = ptx::globaltimer_ns();
     for (int r = 0; r < R; ++r) {
@@ -71,7 +73,7 @@ __device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& 
 
 __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restrict__ local, long long rows, int f16, int rank,
                                                           int R, PeerPtrs dst, PeerPtrs flags, unsigned* counters,
-                                                          int32_t* status) {
+                                                          int32_t* status, int wait) {
     const long long total = rows * f16;
     const long long pitch = (long long)R * f16;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restric
         const uint4 v = local[i];
         for (int r = 0; r < R; ++r) static_cast<uint4*>(dst.p[r])[o] = v;
     }
-    push_handshake(rank, R, flags, counters, status);
+    push_handshake(rank, R, flags, counters, status, wait);
 }
 
 // The SwiGLU gate and the gather that follows it, in one kernel: this rank's slice out[m, j] = T(silu(gu[m, j]) *
@@ -90,7 +92,7 @@ __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restric
 template <typename T>
 __global__ void __launch_bounds__(256) push_gather_swiglu_kernel(const T* __restrict__ gu, long long rows, int F, int rank, int R,
                                                                  PeerPtrs dst, PeerPtrs flags, unsigned* counters,
-                                                                 int32_t* status) {
+                                                                 int32_t* status, int wait) {
     constexpr int V = 16 / (int)sizeof(T);
     const int f16 = F / V;
     const long long total = rows * f16;
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(256) push_gather_swiglu_kernel(const T* __rest
         const long long o = m * pitch + (long long)rank * f16 + c;
         for (int r = 0; r < R; ++r) static_cast<uint4*>(dst.p[r])[o] = oq;
     }
-    push_handshake(rank, R, flags, counters, status);
+    push_handshake(rank, R, flags, counters, status, wait);
 }
 
 }  // namespace
@@ -160,7 +162,7 @@ extern "C" int bi_peer_close(void* ptr) {
 }
 
 extern "C" int bi_push_gather(const void* local, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
-                              int64_t row_bytes, int rank, int world, int32_t* status, void* stream) {
+                              int64_t row_bytes, int rank, int world, int wait, int32_t* status, void* stream) {
     using namespace bi;
     if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world)
         return fail(BI_ERR_BAD_ARG, "bi_push_gather: rank %d of %d (at most %d ranks)", rank, world, MAX_RANKS);
@@ -182,12 +184,12 @@ extern "C" int bi_push_gather(const void* local, void* const* dst, void* const* 
     if (blocks > 128) blocks = 128;
     if (blocks < 1) blocks = 1;
     push_gather_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(local), rows, (int)f16, rank, world, d, f, counters, status);
+        static_cast<const uint4*>(local), rows, (int)f16, rank, world, d, f, counters, status, wait);
     return check_launch("bi_push_gather");
 }
 
 extern "C" int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void* const* flags, uint32_t* counters, int64_t rows,
-                                     int64_t F, int dtype, int rank, int world, int32_t* status, void* stream) {
+                                     int64_t F, int dtype, int rank, int world, int wait, int32_t* status, void* stream) {
     using namespace bi;
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_push_gather_swiglu: dtype %d", dtype);
     if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world)
@@ -210,7 +212,7 @@ extern "C" int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void
     if (blocks > 128) blocks = 128;
     if (blocks < 1) blocks = 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define BI_PGS(TT) push_gather_swiglu_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(gate_up), rows, (int)F, rank, world, d, f, counters, status)
+#define BI_PGS(TT) push_gather_swiglu_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(gate_up), rows, (int)F, rank, world, d, f, counters, status, wait)
     if (dtype == BI_F32) BI_PGS(float); else if (dtype == BI_F16) BI_PGS(__half); else BI_PGS(__nv_bfloat16);
 #undef BI_PGS
     return check_launch("bi_push_gather_swiglu");

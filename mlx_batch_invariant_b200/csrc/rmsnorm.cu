@@ -44,12 +44,40 @@ __device__ __forceinline__ float block_tree_sum(float ss, float* red, int t) {
     return red[0];
 }
 
+// `delta` may be the destination of a peer gather whose arrival nobody has waited for yet: the CTA then first
+// waits (bounded, 2 s) until every peer's flag has reached *epoch; on expiry it records a code and goes on.
+struct NormAwait {
+    const uint32_t* flags;
+    const uint32_t* epoch;
+    int rank, world;
+    int32_t* status;
+};
+
 template <typename T, bool STAGED, bool HAS_W, bool HAS_RES>
 __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __restrict__ delta, const T* __restrict__ w,
-                                                      T* sum_out, T* __restrict__ out, int D, float eps) {
+                                                      T* sum_out, T* __restrict__ out, int D, float eps, NormAwait aw) {
     extern __shared__ uint4 stage_raw[];
     __shared__ float red[TG];
     const int t = threadIdx.x;
+    if (HAS_RES && aw.flags != nullptr) {
+        if (t < aw.world && t != aw.rank) {
+            const uint32_t epoch = *aw.epoch;
+            uint64_t t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            while (true) {
+                uint32_t seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(aw.flags + t) : "memory");
+                if ((int32_t)(seen - epoch) >= 0) break;
+                uint64_t now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (now - t0 > 2000000000ull) {
+                    if (aw.status) atomicCAS(aw.status, 0, (int)(0x20000 | (t << 8) | (epoch & 0xff)));
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
     const size_t row = blockIdx.x;
     const T* xr = x + row * (size_t)D;
     T* orow = out + row * (size_t)D;
@@ -63,7 +91,7 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __res
             const uint4* dsrc = reinterpret_cast<const uint4*>(delta + row * (size_t)D);
             uint4* sdst = reinterpret_cast<uint4*>(sum_out + row * (size_t)D);
             for (int i = t; i < D / VEC; i += TG) {
-                uint4 a = src[i], b = __ldg(dsrc + i);
+                uint4 a = src[i], b = dsrc[i];
                 T* av = reinterpret_cast<T*>(&a);
                 const T* bv = reinterpret_cast<const T*>(&b);
 #pragma unroll
@@ -107,7 +135,7 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __res
 
 template <typename T>
 int launch(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows, int64_t D, float eps,
-           cudaStream_t st) {
+           cudaStream_t st, const NormAwait& aw = NormAwait{nullptr, nullptr, 0, 0, nullptr}) {
     const size_t row_bytes = (size_t)D * sizeof(T);
     const bool staged = row_bytes % 16 == 0 && row_bytes <= 160 * 1024 && aligned(x, 16) && aligned(out, 16) &&
                         (!delta || (aligned(delta, 16) && aligned(sum_out, 16)));
@@ -127,7 +155,7 @@ int launch(const void* x, const void* delta, const void* w, void* sum_out, void*
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "rms_norm smem attr: %s",               \
                                               cudaGetErrorString(e));                               \
         }                                                                                           \
-        kern<<<grid, block, smem, st>>>(xp, dp, wp, sp, op, (int)D, eps);                           \
+        kern<<<grid, block, smem, st>>>(xp, dp, wp, sp, op, (int)D, eps, aw);                           \
     } while (0)
 #define BI_RMS_LAUNCH(ST, HW) do { if (delta) BI_RMS_LAUNCH2(ST, HW, true); else BI_RMS_LAUNCH2(ST, HW, false); } while (0)
     if (staged) { if (w) BI_RMS_LAUNCH(true, true); else BI_RMS_LAUNCH(true, false); }
@@ -170,5 +198,26 @@ extern "C" int bi_add_rms_norm(const void* x, const void* delta, const void* w, 
         case BI_F32: return launch<float>(x, delta, w, sum_out, out, rows, D, eps, st);
         case BI_F16: return launch<__half>(x, delta, w, sum_out, out, rows, D, eps, st);
         default:     return launch<__nv_bfloat16>(x, delta, w, sum_out, out, rows, D, eps, st);
+    }
+}
+
+extern "C" int bi_add_rms_norm_awaiting(const void* x, const void* delta, const void* w, void* sum_out, void* out, int64_t rows,
+                                        int64_t D, float eps, int dtype, void* stream, const uint32_t* flags,
+                                        const uint32_t* epoch, int rank, int world, int32_t* status) {
+    using namespace bi;
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_add_rms_norm_awaiting: dtype %d", dtype);
+    if (rows < 0 || D <= 0 || D > INT32_MAX) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm_awaiting: rows=%lld D=%lld", (long long)rows, (long long)D);
+    if (rows == 0) return BI_OK;
+    if (!x || !delta || !sum_out || !out) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm_awaiting: null pointer");
+    if (out == sum_out || out == x || out == delta) return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm_awaiting: out must not alias x, delta or sum_out");
+    if (rows > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_add_rms_norm_awaiting: rows=%lld exceeds the grid limit", (long long)rows);
+    if (flags && (!epoch || world < 1 || world > 8 || rank < 0 || rank >= world))
+        return fail(BI_ERR_BAD_ARG, "bi_add_rms_norm_awaiting: bad gather to wait for (rank %d of %d)", rank, world);
+    const NormAwait aw{flags, epoch, rank, world, status};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case BI_F32: return launch<float>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
+        case BI_F16: return launch<__half>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
+        default:     return launch<__nv_bfloat16>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
     }
 }

@@ -39,13 +39,15 @@ def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
             and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
 
 
-def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None):
+def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None):
     """``a @ b`` with a batch-invariant reduction order.
 
     ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
     view is fine). fp32 accumulation; the output dtype is the promoted input dtype.
     ``path`` ("auto", "split", "fused", "fold") and ``batch_tile`` (16, 32, 64, 128 batch rows per tile)
-    force a launch shape; all give the same bits.
+    force a launch shape; all give the same bits. ``awaiting`` (flags pointer, epoch pointer, rank, world) says
+    that ``a`` is the destination of a peer gather nobody has waited for yet: the kernel waits for it itself,
+    after it has started streaming the weight (runner/peer.py).
     """
     at, foreign = adopt(a)
     bt, _ = adopt(b)
@@ -75,7 +77,8 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
     lib = _lib.load()
     with torch.cuda.device(dev):
         word, ws, nbytes = _launch_shape(path, batch_tile, M, N, K, lib.bi_matmul_workspace_bytes(M, N, K, code), dev)
-        _lib.check(lib.bi_matmul(a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
-                                 a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code,
-                                 word, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+        args = (a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
+                a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code,
+                word, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(lib.bi_matmul(*args) if awaiting is None else lib.bi_matmul_awaiting(*args, *awaiting))
     return give_back(out.reshape(*lead, N), a, foreign)

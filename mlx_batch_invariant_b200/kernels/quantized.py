@@ -42,7 +42,7 @@ _STAGES = {None: 0, "smem": _lib.QMM_STAGE_SMEM, "tmem": _lib.QMM_STAGE_TMEM}
 
 
 def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, bits: int, path: str = "auto",
-                                     batch_tile: int | None = None, stage: str | None = None):
+                                     batch_tile: int | None = None, stage: str | None = None, awaiting=None):
     """``x @ dequant(w).T``. ``path`` / ``batch_tile`` force a launch shape as for the dense matmul; ``stage``
     ("smem", "tmem") forces how the dequantized weight reaches the tensor core. All give the same bits."""
     xt, foreign = adopt(x)
@@ -68,7 +68,8 @@ def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, b
     lib = _lib.load()
     with torch.cuda.device(dev):
         word, ws, nbytes = _launch_shape(path, batch_tile, M, N, K, lib.bi_qmm_workspace_bytes(M, N, K, code), dev)
-        _lib.check(lib.bi_qmm(x2.data_ptr(), wt.data_ptr(), st.data_ptr(), bt.data_ptr(), out.data_ptr(),
-                              _lib.ptr(ws), nbytes, M, N, K, x2.stride(0) if M > 1 else K, group_size, bits, code,
-                              word | _STAGES[stage], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)))
+        args = (x2.data_ptr(), wt.data_ptr(), st.data_ptr(), bt.data_ptr(), out.data_ptr(),
+                _lib.ptr(ws), nbytes, M, N, K, x2.stride(0) if M > 1 else K, group_size, bits, code,
+                word | _STAGES[stage], _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(lib.bi_qmm(*args) if awaiting is None else lib.bi_qmm_awaiting(*args, *awaiting))
     return give_back(out.reshape(*lead, N), x, foreign)

@@ -99,21 +99,27 @@ class KernelBackend(TorchGlue):
                                          _lib.stream_ptr(gu.device)))
         return out
 
-    def add_rms_norm(self, x, delta, w, eps):
+    fused_wait = True       # the kernels can wait for a peer gather themselves (the *_awaiting entry points)
+
+    def add_rms_norm(self, x, delta, w, eps, awaiting=None):
         from .. import _lib
         x, delta = x.contiguous(), delta.contiguous()
         rows, D = x.shape
         s, out = torch.empty_like(x), torch.empty_like(x)
-        _lib.check(_lib.load().bi_add_rms_norm(x.data_ptr(), delta.data_ptr(), w.data_ptr(), s.data_ptr(), out.data_ptr(),
-                                               rows, D, float(eps), _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(x.device)))
+        args = (x.data_ptr(), delta.data_ptr(), w.data_ptr(), s.data_ptr(), out.data_ptr(), rows, D, float(eps),
+                _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(x.device))
+        if awaiting is None:
+            _lib.check(_lib.load().bi_add_rms_norm(*args))
+        else:
+            _lib.check(_lib.load().bi_add_rms_norm_awaiting(*args, *awaiting, _lib.status_word(x.device).data_ptr()))
         return s, out
 
-    def linear(self, x, w):                      # x[M, K] @ W[N, K]^T
-        return K.batch_invariant_matmul(x, w.T)
+    def linear(self, x, w, awaiting=None):       # x[M, K] @ W[N, K]^T
+        return K.batch_invariant_matmul(x, w.T, awaiting=awaiting)
 
-    def qlinear(self, x, packed, group_size, bits):
+    def qlinear(self, x, packed, group_size, bits, awaiting=None):
         p, s, b = packed
-        return K.batch_invariant_quantized_matmul(x, p, s, b, group_size=group_size, bits=bits)
+        return K.batch_invariant_quantized_matmul(x, p, s, b, group_size=group_size, bits=bits, awaiting=awaiting)
 
     def rms_norm(self, x, w, eps):
         return K.batch_invariant_rms_norm(x, w, eps)
@@ -209,34 +215,56 @@ class ShardedDecoder:
         bits, gs = self.quant
         return quantize_rows(w, gs, bits)
 
-    def _lin(self, x, w):
+    def _add_norm(self, x, delta, w, awaiting=None):
+        if awaiting is None:
+            return self.ops.add_rms_norm(x, delta, w, self.cfg.eps)
+        return self.ops.add_rms_norm(x, delta, w, self.cfg.eps, awaiting=awaiting)
+
+    def _lin(self, x, w, awaiting=None):
+        kw = {} if awaiting is None else {"awaiting": awaiting}
         if self.quant is None:
-            return self.ops.linear(x, w)
-        return self.ops.qlinear(x, w, self.quant[1], self.quant[0])
+            return self.ops.linear(x, w, **kw)
+        return self.ops.qlinear(x, w, self.quant[1], self.quant[0], **kw)
 
     # ---- collectives: join feature slices [M, F/R] -> [M, F], rank-major (the unsharded order)
-    def _gather(self, local):
+    def _gather(self, local, defer=False):
+        """Join this rank's feature slice with the others'. defer=True returns (gathered, awaiting): when the
+        peer gather is in use and the backend's kernels can wait themselves, the gather kernel does not wait for
+        the peers and `awaiting` must be handed to the kernel that reads the result; else `awaiting` is None."""
         if self.world == 1:
-            return local
+            return (local, None) if defer else local
         M, f = local.shape
         local = local.contiguous()
         pg = self._push_gather()
         if pg is not None and pg.fits(M, f * local.element_size()):
-            return pg.gather(local)                      # one launch, result already [M, R*f]
+            if defer and self._fused_wait():
+                return pg.gather(local, wait=False), pg.awaiting()
+            out = pg.gather(local)                       # one launch, result already [M, R*f]
+            return (out, None) if defer else out
+        if defer:
+            return self._gather(local), None
         import torch.distributed as dist
         buf = torch.empty(self.world * M, f, dtype=local.dtype, device=local.device)
         dist.all_gather_into_tensor(buf, local, group=self.group)
         return buf.view(self.world, M, f).permute(1, 0, 2).reshape(M, self.world * f)
 
+    def _fused_wait(self) -> bool:
+        """Whether the kernels that read a gathered activation wait for it themselves (BI_FUSED_WAIT=0 keeps the
+        wait in the gather kernel)."""
+        return (getattr(self.ops, "fused_wait", False) and self.dt != torch.float32
+                and os.environ.get("BI_FUSED_WAIT", "1") != "0")
+
     def _gated(self, gu):
-        """SwiGLU of this rank's gate/up slice, gathered over the ranks: [M, 2F/R] -> [M, F]. With the peer
-        gather the gate is computed inside the gather kernel."""
+        """SwiGLU of this rank's gate/up slice, gathered over the ranks: [M, 2F/R] -> ([M, F], awaiting). With
+        the peer gather the gate is computed inside the gather kernel."""
         if self.world > 1:
             M, f2 = gu.shape
             pg = self._push_gather()
             if pg is not None and gu.is_contiguous() and pg.fits(M, (f2 // 2) * gu.element_size()):
-                return pg.gather_swiglu(gu)
-        return self._gather(self.ops.swiglu(gu))
+                if self._fused_wait():
+                    return pg.gather_swiglu(gu, wait=False), pg.awaiting()
+                return pg.gather_swiglu(gu), None
+        return self._gather(self.ops.swiglu(gu)), None
 
     def _push_gather(self):
         """The peer-memory all-gather (CUDA ranks of one node). BI_GATHER=nccl keeps the library collective,
@@ -281,13 +309,14 @@ class ShardedDecoder:
                 a = self.ops.decode_attention(q, kk, vv, scale)
             else:
                 a = self.ops.prefill_attention(q, kk, vv, scale)
-            a = self._gather(a.transpose(1, 2).reshape(M, self.hq * D))
-            x, h = self.ops.add_rms_norm(x, self._lin(a, L["o"]), L["n2"], cfg.eps)
-            delta = self._gather(self._lin(self._gated(self._lin(h, L["gu"])), L["down"]))
+            a, aw = self._gather(a.transpose(1, 2).reshape(M, self.hq * D), defer=True)
+            x, h = self.ops.add_rms_norm(x, self._lin(a, L["o"], aw), L["n2"], cfg.eps)
+            act, aw = self._gated(self._lin(h, L["gu"]))
             if li + 1 < len(self.layers):       # the add of this block and the first norm of the next, one launch
-                x, h = self.ops.add_rms_norm(x, delta, self.layers[li + 1]["n1"], cfg.eps)
+                delta, aw = self._gather(self._lin(act, L["down"], aw), defer=True)
+                x, h = self._add_norm(x, delta, self.layers[li + 1]["n1"], aw)
             else:
-                x = x + delta
+                x = x + self._gather(self._lin(act, L["down"], aw))
             if self.block_hook is not None:
                 self.block_hook(li, x.reshape(B, T, -1))
         last = x.reshape(B, T, -1)[:, -1]
@@ -325,11 +354,12 @@ class GraphedDecoder:
         for li, L in enumerate(m.layers):
             q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
             a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
-            a = m._gather(a.transpose(1, 2).reshape(B, m.hq * D))
-            x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"]), L["n2"], cfg.eps)
-            delta = m._gather(m._lin(m._gated(m._lin(h, L["gu"])), L["down"]))
+            a, aw = m._gather(a.transpose(1, 2).reshape(B, m.hq * D), defer=True)
+            x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"], aw), L["n2"], cfg.eps)
+            act, aw = m._gated(m._lin(h, L["gu"]))
+            delta, aw = m._gather(m._lin(act, L["down"], aw), defer=True)
             nxt = m.layers[li + 1]["n1"] if li + 1 < len(m.layers) else m.nf
-            x, h = m.ops.add_rms_norm(x, delta, nxt, cfg.eps)
+            x, h = m._add_norm(x, delta, nxt, aw)
         logits = m._gather(m._lin(h, m.head))
         self.tokens.copy_(logits.argmax(-1, keepdim=True))
         self.pos.add_(1)

@@ -84,30 +84,34 @@ class PushGather:
         arr = ctypes.c_void_p * self.world
         return b, arr(*[base + b * self.cap for base in self.bases]), arr(*[base + NBUF * self.cap for base in self.bases])
 
-    def gather_swiglu(self, gate_up: torch.Tensor) -> torch.Tensor:
+    def awaiting(self):
+        """What a consumer kernel needs to wait for the gather just issued with wait=False: this rank's flag
+        array, the device word holding the gather's epoch, rank and world (the trailing arguments of the
+        *_awaiting entry points)."""
+        return (self.bases[self.rank] + NBUF * self.cap, self.counters.data_ptr() + 4, self.rank, self.world)
+
+    def gather_swiglu(self, gate_up: torch.Tensor, wait: bool = True) -> torch.Tensor:
         """gate_up[rows, 2F] of this rank -> swiglu of every rank's slice, [rows, world * F]: the gate is computed
-        while the slice is pushed (one launch; same bits as swiglu followed by gather)."""
+        while the slice is pushed (one launch; same bits as swiglu followed by gather). wait=False: see gather()."""
         rows, f2 = gate_up.shape
         F = f2 // 2
         b, dst, flags = self._slot()
         status = _lib.status_word(self.dev)
         _lib.check(self.lib.bi_push_gather_swiglu(gate_up.data_ptr(), dst, flags, self.counters.data_ptr(), rows, F,
-                                                  _lib.DTYPE_CODE[gate_up.dtype], self.rank, self.world, status.data_ptr(),
+                                                  _lib.DTYPE_CODE[gate_up.dtype], self.rank, self.world, int(wait), status.data_ptr(),
                                                   _lib.stream_ptr(self.dev)))
         n = rows * F * gate_up.element_size() * self.world
         return self.own[b][:n].view(gate_up.dtype).view(rows, self.world * F)
 
-    def gather(self, local: torch.Tensor) -> torch.Tensor:
-        """local[rows, f] (contiguous) -> [rows, world * f], rank-major along the feature axis."""
+    def gather(self, local: torch.Tensor, wait: bool = True) -> torch.Tensor:
+        """local[rows, f] (contiguous) -> [rows, world * f], rank-major along the feature axis. wait=False: the
+        kernel does not wait for the peers' slices; the NEXT kernel on the stream that reads the result must be
+        an *_awaiting one given ``self.awaiting()``."""
         rows, f = local.shape
         row_bytes = f * local.element_size()
-        b = self.calls % self.mod
-        self.calls += 1
-        arr = ctypes.c_void_p * self.world
-        dst = arr(*[base + b * self.cap for base in self.bases])
-        flags = arr(*[base + NBUF * self.cap for base in self.bases])
+        b, dst, flags = self._slot()
         status = _lib.status_word(self.dev)
         _lib.check(self.lib.bi_push_gather(local.data_ptr(), dst, flags, self.counters.data_ptr(), rows, row_bytes,
-                                           self.rank, self.world, status.data_ptr(), _lib.stream_ptr(self.dev)))
+                                           self.rank, self.world, int(wait), status.data_ptr(), _lib.stream_ptr(self.dev)))
         n = rows * row_bytes * self.world
         return self.own[b][:n].view(local.dtype).view(rows, self.world * f)
