@@ -69,6 +69,13 @@ int bi_read_device_status(const int32_t* status, int32_t* host_value, void* stre
 int bi_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t D, float eps,
                 int dtype, void* stream);
 
+/* LayerNorm: out[r, :] = T((((x[r, :] - mean) * rsqrt(var + eps)) * w) + b), mean and variance of the row by
+ * fixed-stride fp32 partials and the fixed tree of bi_rms_norm (two passes: sum, then squared deviations).
+ * No kernel in the reference yet -- it lists a batch-invariant LayerNorm as future work (README.md:261-263); the
+ * call it would replace is the framework's layer_norm. x, out: [rows, D] contiguous; w, b: [D] or NULL. */
+int bi_layer_norm(const void* x, const void* w, const void* b, void* out, int64_t rows, int64_t D, float eps,
+                  int dtype, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Dense matmul: out[M, N] = a[M, K] @ b[K, N], K folded in 256-wide groups. *
  * replaces batch_invariant_matmul / launch_tiled / bi_matmul_* /            *
@@ -102,6 +109,14 @@ size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
 int bi_matmul(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes,
               int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk,
               int64_t b_sn, int dtype, int path, int32_t* status, void* stream);
+
+/* bi_matmul with the bias of a linear layer added in the epilogue: out[m, n] = T(float(T(total)) + float(bias[n])),
+ * bias: [N] in the output dtype (NULL = none). The bits of the reference's addmm with alpha = beta = 1
+ * (mlx_batch_invariant/ops.py:54-62: the product is rounded to the output dtype, then c is added elementwise),
+ * without the second pass over the output; the reference names this fusion as future work (README.md:261-263). */
+int bi_matmul_bias(const void* a, const void* b, const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                   int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn,
+                   int dtype, int path, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Affine quantized matmul: out[M, N] = x[M, K] @ dequant(w)[N, K]^T         *

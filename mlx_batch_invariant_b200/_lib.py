@@ -36,9 +36,12 @@ SIGNATURES = {
     "bi_launch_count": (ctypes.c_ulonglong, []),
     "bi_read_device_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
     "bi_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
+    "bi_layer_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "bi_matmul_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int]),
     "bi_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64, c_int64, c_int64,
                           c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "bi_matmul_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64, c_int64, c_int64,
+                               c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "bi_qmm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int]),
     "bi_qmm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64,
                        c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -147,7 +150,8 @@ def matmul_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     ws = _workspaces.get(key)
     need = max(nbytes, COUNTER_BYTES)
     if ws is None or ws.numel() < need:
-        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        ws[:COUNTER_BYTES].zero_()       # only the counters have to start at zero (and a capture records only this small fill)
         _workspaces[key] = ws
     return ws
 

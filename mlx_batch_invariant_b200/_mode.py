@@ -7,7 +7,7 @@ code reaches for and restores them on leaving it, under one process-global lock;
 
 Patched while the mode is on:
   * PyTorch: ``torch.matmul``, ``torch.mm``, ``torch.addmm``, ``Tensor.__matmul__`` /
-    ``__rmatmul__`` / ``.matmul`` / ``.mm``, ``F.linear``, ``F.rms_norm``,
+    ``__rmatmul__`` / ``.matmul`` / ``.mm``, ``F.linear``, ``F.rms_norm``, ``F.layer_norm``,
     ``F.scaled_dot_product_attention`` -- what ``nn.Linear``, ``nn.RMSNorm`` and attention
     modules call.
   * MLX, when ``mlx.core`` is importable: the six symbols the reference patches
@@ -45,6 +45,7 @@ def _torch_patches():
         (torch.Tensor, "mm", ops.torch_tensor_matmul),
         (F, "linear", ops.torch_linear),
         (F, "rms_norm", ops.torch_rms_norm),
+        (F, "layer_norm", ops.torch_layer_norm),
         (F, "scaled_dot_product_attention", ops.torch_sdpa),
     ]
 

@@ -71,4 +71,13 @@ template <> struct Cvt<__half> {
     static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
 };
 
+// Final rounding of an output element, with the optional bias of a linear layer: T(total), then -- as an
+// elementwise add of two T arrays would -- T(float(T(total)) + float(bias)). Two roundings, the bits of the unfused
+// sequence (product rounded to the output type first, bias added afterwards: mlx_batch_invariant/ops.py:54-62).
+template <typename T>
+__device__ __forceinline__ T round_out(float total, const T* bias, long long n) {
+    const T r = Cvt<T>::down(total);
+    return bias ? Cvt<T>::down(add_rn(Cvt<T>::up(r), Cvt<T>::up(bias[n]))) : r;
+}
+
 }  // namespace bi

@@ -22,7 +22,7 @@ int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 // tiles 14.8 against 14.5 us). Below that the K groups are spread over CTAs (split) while the fp32 partials
 // stay L2-sized.
 TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
-    TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO, Await{nullptr, nullptr, 0, 0}};
+    TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO, Await{nullptr, nullptr, 0, 0}, nullptr};
     const int64_t G = ngroups(K);
     const int64_t nt = (N + 127) / 128;
     const int64_t fill = (int64_t)sm_count() * 4 / 5;
@@ -94,6 +94,7 @@ int simt_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int
     const size_t head = pa.zeroed ? COUNTER_BYTES : 0;
     const size_t need = head + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
     *part = nullptr;
+    if (*split && pa.kind == BI_MATMUL_AUTO && (!ws || ws_bytes < need)) *split = false;   // AUTO: fold in place instead
     if (!*split) return BI_OK;
     if (!ws || ws_bytes < need) return fail(BI_ERR_WORKSPACE, "%s: split path needs %zu workspace bytes, got %zu", op, need, ws_bytes);
     if (!aligned(ws, 16)) return fail(BI_ERR_MISALIGNED, "%s: workspace must be 16-byte aligned", op);
@@ -106,12 +107,14 @@ int simt_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int
 
 extern "C" size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
     using namespace bi;
-    (void)dtype;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    // Enough for whichever shape AUTO may pick, with or without a counter block in front; a forced
-    // BI_MATMUL_SPLIT always needs ceil(K/256) * M * N * 4 bytes (+ BI_MATMUL_COUNTER_BYTES with BI_MATMUL_WS_ZEROED).
+    // Enough for the shape AUTO picks, with or without a counter block in front; a forced BI_MATMUL_SPLIT always
+    // needs ceil(K/256) * M * N * 4 bytes (+ BI_MATMUL_COUNTER_BYTES with BI_MATMUL_WS_ZEROED). 16-bit weights follow
+    // the tensor-core rule (a 16-bit weight that has to take the CUDA-core path folds in place under AUTO when the
+    // workspace is too small for its split); fp32 follows the CUDA-core rule.
     if (ngroups(K) <= 1) return 0;
-    if (M > SPLIT_M_MAX && !tc_auto_shape(M, N, K).split) return 0;
+    const bool split = dtype == BI_F32 ? simt_auto_split(M, K) : tc_auto_shape(M, N, K).split;
+    if (!split) return 0;
     return COUNTER_BYTES + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
 }
 
@@ -130,7 +133,7 @@ int check_await(const char* op, const Await& aw) {
 
 int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
                 int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
-                int path, int32_t* status, void* stream, const Await& aw) {
+                int path, int32_t* status, void* stream, const Await& aw, const void* bias = nullptr) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dtype %d", dtype);
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_matmul: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return BI_OK;
@@ -155,16 +158,17 @@ int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t
         rc = tc_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
         if (rc) return rc;
         sh.await = aw;
+        sh.bias = bias;
         const int64_t w_ld = N == 1 ? K : b_sn;
         rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
-        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
+        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, bias, N);
     }
     if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_awaiting: only weights on the tensor-core path can wait for a gather");
     bool split;
     rc = simt_shape("bi_matmul", pa, workspace, workspace_bytes, M, N, K, &split, &part);
     if (rc) return rc;
-    return launch_simt_matmul(a, b, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, split, st);
+    return launch_simt_matmul(a, b, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, split, st, bias);
 }
 }  // namespace
 }  // namespace bi
@@ -174,6 +178,15 @@ extern "C" int bi_matmul(const void* a, const void* b, void* out, void* workspac
                          int path, int32_t* status, void* stream) {
     return bi::matmul_impl(a, b, out, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream,
                            bi::Await{nullptr, nullptr, 0, 0});
+}
+
+extern "C" int bi_matmul_bias(const void* a, const void* b, const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                              int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
+                              int path, int32_t* status, void* stream) {
+    if (bias && !bi::aligned(bias, bi::dtype_ok(dtype) ? bi::dtype_size(dtype) : 1))
+        return bi::fail(BI_ERR_MISALIGNED, "bi_matmul_bias: bias is not aligned to its element size");
+    return bi::matmul_impl(a, b, out, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream,
+                           bi::Await{nullptr, nullptr, 0, 0}, bias);
 }
 
 extern "C" int bi_matmul_awaiting(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,

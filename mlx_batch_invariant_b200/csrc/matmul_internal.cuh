@@ -6,12 +6,14 @@
 namespace bi {
 
 // Split-path fold: out[i] = T(((0 + part[0][i]) + part[1][i]) + ...), part is [G][MN] fp32.
-int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st);
+// bias: optional [N] in the output dtype (N = row length of out), added after the rounding.
+int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias = nullptr,
+                   int64_t N = 1);
 
 // CUDA-core path (fp32 inputs, or weights TMA cannot address).
 int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,
                        int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, bool split,
-                       cudaStream_t st);
+                       cudaStream_t st, const void* bias = nullptr);
 int launch_simt_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out, float* part,
                     int64_t M, int64_t N, int64_t K, int64_t x_sm, int gs, int bits, int dtype, bool split,
                     cudaStream_t st);
@@ -48,6 +50,7 @@ struct TcShape {
     unsigned* counters;
     int stage;
     Await await;
+    const void* bias;     // optional [N] bias in the output dtype, added after the output's rounding
 };
 int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, const TcQuant* q, void* out,
                      float* part, int64_t M, int64_t N, int64_t K, int dtype, const TcShape& shape, int32_t* status,

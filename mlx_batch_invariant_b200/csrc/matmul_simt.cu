@@ -35,6 +35,7 @@ struct QuantArgs {
     const void* scales;  // [N, K/gs]
     const void* biases;
     int bits, gs;
+    const void* out_bias;  // optional [N] bias of the linear layer (dense and quantized alike), in T
 };
 
 // TM rows x 4 columns per thread; tile = (16*TM) x 64.
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restric
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (SPLIT) static_cast<float*>(outp)[((int64_t)g0 * M + m) * N + n] = total[i][j];
-            else static_cast<T*>(outp)[(int64_t)m * N + n] = Cvt<T>::down(total[i][j]);
+            else static_cast<T*>(outp)[(int64_t)m * N + n] = round_out<T>(total[i][j], static_cast<const T*>(qa.out_bias), n);
         }
     }
 }
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restric
 // (reference: bi_matmul_combine, mlx_batch_invariant/kernels/matmul.py:226-234).
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ part, T* __restrict__ out, int G,
-                                                      int64_t MN) {
+                                                      int64_t MN, const T* __restrict__ bias, int64_t N) {
     const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i0 >= MN) return;
     float total[VEC];
@@ -151,20 +152,21 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
         }
     }
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) out[i0 + v] = Cvt<T>::down(total[v]);
+    for (int v = 0; v < VEC; ++v) out[i0 + v] = round_out<T>(total[v], bias, bias ? (i0 + v) % N : 0);
 }
 
 template <typename T>
-int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st) {
+int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st, const void* bias_v, int64_t N) {
+    const T* bias = static_cast<const T*>(bias_v);
     if (MN % 4 == 0 && aligned(part, 16) && MN < (1 << 20)) {
         // few outputs: one per thread, so that enough loads are in flight to cover the L2 latency
         // (4096x14336 at M = 16: 31.1 -> 28.3 us for matmul + combine)
-        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN);
+        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
     } else if (MN % 4 == 0 && aligned(part, 16)) {
         const int64_t threads = MN / 4;
-        combine_kernel<T, 4><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN);
+        combine_kernel<T, 4><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
     } else {
-        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN);
+        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
     }
     return check_launch("matmul combine");
 }
@@ -186,23 +188,23 @@ int simt_t(const void* a, const void* b, const QuantArgs& qa, void* out, float* 
 #undef BI_SIMT
     int rc = check_launch("matmul (cuda-core path)");
     if (rc || !split) return rc;
-    return combine_t<T>(part, out, G, M * N, st);
+    return combine_t<T>(part, out, G, M * N, st, qa.out_bias, N);
 }
 
 }  // namespace
 
-int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st) {
+int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias, int64_t N) {
     switch (dtype) {
-        case BI_F32: return combine_t<float>(part, out, G, MN, st);
-        case BI_F16: return combine_t<__half>(part, out, G, MN, st);
-        default:     return combine_t<__nv_bfloat16>(part, out, G, MN, st);
+        case BI_F32: return combine_t<float>(part, out, G, MN, st, bias, N);
+        case BI_F16: return combine_t<__half>(part, out, G, MN, st, bias, N);
+        default:     return combine_t<__nv_bfloat16>(part, out, G, MN, st, bias, N);
     }
 }
 
 int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,
                        int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, bool split,
-                       cudaStream_t st) {
-    QuantArgs qa{nullptr, nullptr, nullptr, 0, 0};
+                       cudaStream_t st, const void* bias) {
+    QuantArgs qa{nullptr, nullptr, nullptr, 0, 0, bias};
     switch (dtype) {
         case BI_F32: return simt_t<float, false>(a, b, qa, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, split, st);
         case BI_F16: return simt_t<__half, false>(a, b, qa, out, part, M, N, K, a_sm, a_sk, b_sk, b_sn, split, st);
@@ -213,7 +215,7 @@ int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int
 int launch_simt_qmm(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out, float* part,
                     int64_t M, int64_t N, int64_t K, int64_t x_sm, int gs, int bits, int dtype, bool split,
                     cudaStream_t st) {
-    QuantArgs qa{w, scales, biases, bits, gs};
+    QuantArgs qa{w, scales, biases, bits, gs, nullptr};
     switch (dtype) {
         case BI_F32: return simt_t<float, true>(x, nullptr, qa, out, part, M, N, K, x_sm, 1, 1, K, split, st);
         case BI_F16: return simt_t<__half, true>(x, nullptr, qa, out, part, M, N, K, x_sm, 1, 1, K, split, st);

@@ -103,6 +103,7 @@ struct Params {
     const void* scales; // quantized only: [N, K/gs] in T
     const void* biases;
     int32_t* status;
+    const void* bias;   // optional [N] in T, added to the rounded output (fused and in-kernel-fold shapes)
     Await await;        // activation produced by a peer gather that has not been waited for (flags == nullptr: none)
     unsigned* counters; // split path with in-kernel fold: one arrival counter per (weight tile, batch tile), zero between calls
     int M, N, K, G;
@@ -607,6 +608,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             return r;
         };
         T* out = static_cast<T*>(p.out);
+        const T* bias = static_cast<const T*>(p.bias);
         float small_total[8];                                        // running totals of a tile of at most 8 batch rows (fused)
 #pragma unroll
         for (int j = 0; j < 8; ++j) small_total[j] = 0.0f;
@@ -646,7 +648,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         if (last && n < p.N) {
 #pragma unroll
                             for (int j = 0; j < W; ++j)
-                                if (j < ncols) out[(long long)(m0 + j) * p.N + n] = Cvt<T>::down(small_total[j]);
+                                if (j < ncols) out[(long long)(m0 + j) * p.N + n] = round_out<T>(small_total[j], bias, n);
                         }
                     }
                 }
@@ -716,7 +718,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                             }
 #pragma unroll
                             for (int u = 0; u < 4; ++u)
-                                if (mm + u < ncols) out[(long long)(m0 + mm + u) * p.N + n] = Cvt<T>::down(tot[u]);
+                                if (mm + u < ncols) out[(long long)(m0 + mm + u) * p.N + n] = round_out<T>(tot[u], bias, n);
                         }
                     }
                 }
@@ -743,7 +745,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
                         for (int j = 0; j < EW; ++j) {
                             const int m = m0 + c * EW + j;
-                            if (c * EW + j < ncols) out[(long long)m * p.N + n] = Cvt<T>::down(__uint_as_float(t[j]));
+                            if (c * EW + j < ncols) out[(long long)m * p.N + n] = round_out<T>(__uint_as_float(t[j]), bias, n);
                         }
                     }
                 } else {
@@ -1058,6 +1060,7 @@ int launch_tc_matmul(const void* x, int64_t x_ld, const void* w, int64_t w_ld, c
     Params p{};
     p.out = out; p.part = part; p.status = status;
     p.await = shape.await;
+    p.bias = shape.bias;
     p.counters = split ? shape.counters : nullptr;
     p.scales = quant ? q->scales : nullptr; p.biases = quant ? q->biases : nullptr;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;

@@ -111,19 +111,46 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __res
     }
     const T* xin = STAGED ? xs : (HAS_RES ? sum_out + row * (size_t)D : xr);
 
+    // Rows of up to 256 * KEEP elements keep the thread's values in registers between the two passes (the second
+    // pass then reads neither shared nor global memory for x); longer rows read them again.
+    constexpr int KEEP = 16;
+    const bool keep = D <= TG * KEEP;
+    float kept[KEEP];
     float ss = 0.0f;
-    for (int i = t; i < D; i += TG) {
-        float v = Cvt<T>::up(xin[i]);
-        ss = fma_rn(v, v, ss);
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = t + j * TG;
+            kept[j] = i < D ? Cvt<T>::up(xin[i]) : 0.0f;
+            if (i < D) ss = fma_rn(kept[j], kept[j], ss);
+        }
+    } else {
+        for (int i = t; i < D; i += TG) {
+            float v = Cvt<T>::up(xin[i]);
+            ss = fma_rn(v, v, ss);
+        }
     }
     const float total = block_tree_sum(ss, red, t);
     const float inv = rsqrt_canon(add_rn(div_canon(total, (float)D), eps));
 
-    for (int i = t; i < D; i += TG) {
-        float v = mul_rn(Cvt<T>::up(xin[i]), inv);
-        float wi = HAS_W ? Cvt<T>::up(w[i]) : 1.0f;
-        T o = Cvt<T>::down(mul_rn(v, wi));
-        if (STAGED) xs[i] = o; else orow[i] = o;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = t + j * TG;
+            if (i < D) {
+                const float v = mul_rn(kept[j], inv);
+                const float wi = HAS_W ? Cvt<T>::up(w[i]) : 1.0f;
+                const T o = Cvt<T>::down(mul_rn(v, wi));
+                if (STAGED) xs[i] = o; else orow[i] = o;
+            }
+        }
+    } else {
+        for (int i = t; i < D; i += TG) {
+            float v = mul_rn(Cvt<T>::up(xin[i]), inv);
+            float wi = HAS_W ? Cvt<T>::up(w[i]) : 1.0f;
+            T o = Cvt<T>::down(mul_rn(v, wi));
+            if (STAGED) xs[i] = o; else orow[i] = o;
+        }
     }
     if (STAGED) {
         constexpr int VEC = 16 / sizeof(T);
@@ -131,6 +158,77 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __res
         uint4* dst = reinterpret_cast<uint4*>(orow);
         for (int i = t; i < D / VEC; i += TG) dst[i] = stage_raw[i];
     }
+}
+
+// LayerNorm, one CTA of 256 threads per row, in the manner of the RMSNorm above (the reference lists a
+// batch-invariant LayerNorm as future work, README.md:261-263 there; this is its canonical order here):
+//   thread t:  s_t = 0;  for i = t, t+256, ...: s_t = s_t + x_i           tree 128..1 -> mean = sum / float(D)
+//   thread t:  q_t = 0;  for i = t, t+256, ...: d = x_i - mean; q_t = fma(d, d, q_t)   tree -> var = q / float(D)
+//   inv = 1 / sqrt(var + eps);  out_i = T((((x_i - mean) * inv) * w_i) + b_i)   (w, b optional; one rounding)
+template <typename T, bool HAS_W, bool HAS_B>
+__global__ void __launch_bounds__(TG) layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                                        T* __restrict__ out, int D, float eps) {
+    __shared__ float red[TG];
+    const int t = threadIdx.x;
+    const T* xr = x + (size_t)blockIdx.x * (size_t)D;
+    T* orow = out + (size_t)blockIdx.x * (size_t)D;
+    constexpr int KEEP = 16;                     // rows of up to 4096 elements stay in registers after the first read
+    const bool keep = D <= TG * KEEP;
+    float kept[KEEP];
+    float s = 0.0f;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = t + j * TG;
+            kept[j] = i < D ? Cvt<T>::up(xr[i]) : 0.0f;
+            if (i < D) s = add_rn(s, kept[j]);
+        }
+    } else {
+        for (int i = t; i < D; i += TG) s = add_rn(s, Cvt<T>::up(xr[i]));
+    }
+    const float mean = div_canon(block_tree_sum(s, red, t), (float)D);
+    __syncthreads();                             // red[] is reused by the second reduction
+    float q = 0.0f;
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = t + j * TG;
+            if (i < D) { const float d = sub_rn(kept[j], mean); q = fma_rn(d, d, q); }
+        }
+    } else {
+        for (int i = t; i < D; i += TG) { const float d = sub_rn(Cvt<T>::up(xr[i]), mean); q = fma_rn(d, d, q); }
+    }
+    const float var = div_canon(block_tree_sum(q, red, t), (float)D);
+    const float inv = rsqrt_canon(add_rn(var, eps));
+    auto finish = [&](float xv, int i) {
+        float y = mul_rn(sub_rn(xv, mean), inv);
+        if (HAS_W) y = mul_rn(y, Cvt<T>::up(w[i]));
+        if (HAS_B) y = add_rn(y, Cvt<T>::up(b[i]));
+        orow[i] = Cvt<T>::down(y);
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = t + j * TG;
+            if (i < D) finish(kept[j], i);
+        }
+    } else {
+        for (int i = t; i < D; i += TG) finish(Cvt<T>::up(xr[i]), i);
+    }
+}
+
+template <typename T>
+int launch_layer_norm(const void* x, const void* w, const void* b, void* out, int64_t rows, int64_t D, float eps, cudaStream_t st) {
+    const T* xp = static_cast<const T*>(x);
+    const T* wp = static_cast<const T*>(w);
+    const T* bp = static_cast<const T*>(b);
+    T* op = static_cast<T*>(out);
+    dim3 grid((unsigned)rows), block(TG);
+    if (w && b) layer_norm_kernel<T, true, true><<<grid, block, 0, st>>>(xp, wp, bp, op, (int)D, eps);
+    else if (w) layer_norm_kernel<T, true, false><<<grid, block, 0, st>>>(xp, wp, bp, op, (int)D, eps);
+    else if (b) layer_norm_kernel<T, false, true><<<grid, block, 0, st>>>(xp, wp, bp, op, (int)D, eps);
+    else layer_norm_kernel<T, false, false><<<grid, block, 0, st>>>(xp, wp, bp, op, (int)D, eps);
+    return check_launch("bi_layer_norm");
 }
 
 template <typename T>
@@ -219,5 +317,21 @@ extern "C" int bi_add_rms_norm_awaiting(const void* x, const void* delta, const 
         case BI_F32: return launch<float>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
         case BI_F16: return launch<__half>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
         default:     return launch<__nv_bfloat16>(x, delta, w, sum_out, out, rows, D, eps, st, aw);
+    }
+}
+
+extern "C" int bi_layer_norm(const void* x, const void* w, const void* b, void* out, int64_t rows, int64_t D, float eps,
+                             int dtype, void* stream) {
+    using namespace bi;
+    if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_layer_norm: dtype %d", dtype);
+    if (rows < 0 || D <= 0 || D > INT32_MAX) return fail(BI_ERR_BAD_ARG, "bi_layer_norm: rows=%lld D=%lld", (long long)rows, (long long)D);
+    if (rows == 0) return BI_OK;
+    if (!x || !out) return fail(BI_ERR_BAD_ARG, "bi_layer_norm: null pointer");
+    if (rows > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_layer_norm: rows=%lld exceeds the grid limit", (long long)rows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case BI_F32: return launch_layer_norm<float>(x, w, b, out, rows, D, eps, st);
+        case BI_F16: return launch_layer_norm<__half>(x, w, b, out, rows, D, eps, st);
+        default:     return launch_layer_norm<__nv_bfloat16>(x, w, b, out, rows, D, eps, st);
     }
 }

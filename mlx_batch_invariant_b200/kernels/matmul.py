@@ -39,7 +39,7 @@ def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
             and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
 
 
-def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None):
+def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None, bias=None):
     """``a @ b`` with a batch-invariant reduction order.
 
     ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
@@ -47,7 +47,8 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
     ``path`` ("auto", "split", "fused", "fold") and ``batch_tile`` (16, 32, 64, 128 batch rows per tile)
     force a launch shape; all give the same bits. ``awaiting`` (flags pointer, epoch pointer, rank, world) says
     that ``a`` is the destination of a peer gather nobody has waited for yet: the kernel waits for it itself,
-    after it has started streaming the weight (runner/peer.py).
+    after it has started streaming the weight (runner/peer.py). ``bias`` ([N], the output dtype) is added to the
+    rounded product in the kernel's epilogue: the bits of ``batch_invariant_matmul(a, b) + bias``.
     """
     at, foreign = adopt(a)
     bt, _ = adopt(b)
@@ -80,5 +81,12 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
         args = (a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
                 a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code,
                 word, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
-        _lib.check(lib.bi_matmul(*args) if awaiting is None else lib.bi_matmul_awaiting(*args, *awaiting))
+        if bias is not None:
+            bias_t = adopt(bias)[0]
+            if bias_t.shape != (N,) or bias_t.dtype != out_dtype or not bias_t.is_cuda or awaiting is not None:
+                raise ValueError("bias must be a CUDA tensor of shape [N] in the output dtype (and cannot be combined with awaiting)")
+            bias_t = bias_t.contiguous()
+            _lib.check(lib.bi_matmul_bias(args[0], args[1], bias_t.data_ptr(), *args[2:]))
+        else:
+            _lib.check(lib.bi_matmul(*args) if awaiting is None else lib.bi_matmul_awaiting(*args, *awaiting))
     return give_back(out.reshape(*lead, N), a, foreign)

@@ -25,6 +25,7 @@ from .kernels import (
     batch_invariant_quantized_matmul,
     batch_invariant_rms_norm,
 )
+from .kernels import batch_invariant_layer_norm
 from .kernels import attention as _attn
 from .kernels import quantized as _quant
 
@@ -34,6 +35,7 @@ _orig_mm = torch.mm
 _orig_addmm = torch.addmm
 _orig_linear = F.linear
 _orig_rms_norm = F.rms_norm
+_orig_layer_norm = F.layer_norm
 _orig_sdpa = F.scaled_dot_product_attention
 _orig_tensor_matmul = torch.Tensor.__matmul__
 _orig_tensor_rmatmul = torch.Tensor.__rmatmul__
@@ -85,6 +87,9 @@ def addmm(c, a, b, /, alpha: float = 1.0, beta: float = 1.0, *, stream=None):
     reason = _mm_reason(a, b)
     if reason is None:
         handled["addmm"] += 1
+        if (alpha == 1.0 and beta == 1.0 and isinstance(c, torch.Tensor) and c.is_cuda and c.ndim == 1
+                and c.shape[0] == b.shape[1] and c.dtype == torch.result_type(a, b)):
+            return batch_invariant_matmul(a, b, bias=c)      # a linear layer's bias: added in the kernel's epilogue, same bits
         prod = batch_invariant_matmul(a, b)
         if alpha != 1.0:
             prod = prod * alpha
@@ -205,6 +210,20 @@ def torch_sdpa(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False
     _fallback("sdpa", "array-mask" if isinstance(attn_mask, torch.Tensor) else "sinks-or-shape")
     return _orig_sdpa(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale,
                       enable_gqa=enable_gqa)
+
+
+def torch_layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5):
+    """F.layer_norm over the last axis (an extension: the reference does not patch a LayerNorm; counted under
+    ``layer_norm``)."""
+    shape = tuple(normalized_shape) if not isinstance(normalized_shape, int) else (normalized_shape,)
+    if len(shape) == 1 and shape[0] == input.shape[-1] and _is_float(input):
+        if _on_cuda(input, weight, bias):
+            handled["layer_norm"] += 1
+            return batch_invariant_layer_norm(input, weight, bias, eps)
+        _fallback("layer_norm", "not-cuda")
+    else:
+        _fallback("layer_norm", "non-float")
+    return _orig_layer_norm(input, normalized_shape, weight, bias, eps)
 
 
 def reset_stats():

@@ -115,6 +115,40 @@ void orc_rms_norm(const void* x, const void* w, void* out, int64_t rows, int64_t
     }
 }
 
+/* LayerNorm in the manner of orc_rms_norm. The reference has no LayerNorm kernel (it names one as future work,
+ * README.md:261-263); this states the order the CUDA kernel defines: stride-256 fp32 partial sums and the same tree
+ * for the mean, then for the squared deviations; out = T((((x - mean) * inv) * w) + b), one rounding. */
+void orc_layer_norm(const void* x, const void* w, const void* b, void* out, int64_t rows, int64_t D, float eps, int dt) {
+    enum { TG = 256 };
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float red[TG];
+        const int64_t base = r * D;
+        for (int t = 0; t < TG; ++t) {
+            float s = 0.0f;
+            for (int64_t i = t; i < D; i += TG) s = s + load_el(x, base + i, dt);
+            red[t] = s;
+        }
+        for (int s = TG / 2; s > 0; s >>= 1)
+            for (int t = 0; t < s; ++t) red[t] = red[t] + red[t + s];
+        const float mean = red[0] / (float)D;
+        for (int t = 0; t < TG; ++t) {
+            float q = 0.0f;
+            for (int64_t i = t; i < D; i += TG) { float d = load_el(x, base + i, dt) - mean; q = fmaf(d, d, q); }
+            red[t] = q;
+        }
+        for (int s = TG / 2; s > 0; s >>= 1)
+            for (int t = 0; t < s; ++t) red[t] = red[t] + red[t + s];
+        const float inv = orc_rsqrt(red[0] / (float)D + eps);
+        for (int64_t i = 0; i < D; ++i) {
+            float y = (load_el(x, base + i, dt) - mean) * inv;
+            if (w) y = y * load_el(w, i, dt);
+            if (b) y = y + load_el(b, i, dt);
+            store_el(out, base + i, dt, y);
+        }
+    }
+}
+
 /* ---- attention ---------------------------------------------------------------------- */
 #define MAXD 256
 typedef struct { float m, l, acc[MAXD]; } split_state;

@@ -39,6 +39,7 @@ def lib() -> ctypes.CDLL:
                                           c_int64, c_int64, c_int]
         L.orc_combine.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int]
         L.orc_dequant.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int]
+        L.orc_layer_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int]
         L.orc_set_threads.restype = c_int
         L.orc_set_threads.argtypes = [c_int]
         _lib = L
@@ -70,6 +71,17 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> torch.Tenso
     out = torch.empty_like(x)
     lib().orc_rms_norm(x.data_ptr(), None if w is None else w.data_ptr(), out.data_ptr(), x.numel() // D, D,
                        float(eps), ORC[x.dtype])
+    return out
+
+
+def layer_norm(x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None, eps: float) -> torch.Tensor:
+    x = _c(x)
+    D = x.shape[-1]
+    w = None if w is None else _c(w.to(x.dtype))
+    b = None if b is None else _c(b.to(x.dtype))
+    out = torch.empty_like(x)
+    lib().orc_layer_norm(x.data_ptr(), None if w is None else w.data_ptr(), None if b is None else b.data_ptr(),
+                         out.data_ptr(), x.numel() // D, D, float(eps), ORC[x.dtype])
     return out
 
 
@@ -140,6 +152,16 @@ def rms_norm_f64(x: torch.Tensor, w: torch.Tensor | None, eps: float) -> np.ndar
     xf = _f64(x)
     inv = 1.0 / np.sqrt((xf * xf).mean(-1, keepdims=True) + eps)
     return xf * inv * (1.0 if w is None else _f64(w))
+
+
+def layer_norm_f64(x: torch.Tensor, w: torch.Tensor | None, b: torch.Tensor | None, eps: float) -> np.ndarray:
+    xf = _f64(x)
+    y = (xf - xf.mean(-1, keepdims=True)) / np.sqrt(xf.var(-1, keepdims=True) + eps)
+    if w is not None:
+        y = y * _f64(w)
+    if b is not None:
+        y = y + _f64(b)
+    return y
 
 
 def unpack_codes(w: torch.Tensor, bits: int) -> np.ndarray:

@@ -280,3 +280,27 @@ def test_quantized_weight_row_position_independence(bi):
     for off, n in [(0, 384), (384, 384), (128, 128), (40, 200)]:
         part = bi.batch_invariant_quantized_matmul(x, pc[off:off + n], sc[off:off + n], bc[off:off + n], group_size=64, bits=4)
         assert R.bits_of(part) == R.bits_of(full[:, off:off + n].contiguous()), (off, n)
+
+
+# ---- bias in the epilogue ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_bias_epilogue_gives_the_bits_of_matmul_then_add(bi, dt):
+    """A linear layer's bias added inside the kernel (every launch shape, both matmul paths) equals the unfused
+    sequence bit for bit: the product rounded to the output dtype, then an elementwise add."""
+    for M, N, K in [(1, 384, 1024), (9, 200, 520), (64, 4096, 4096), (130, 512, 768)]:
+        x, w = xw(M, N, K, dt, M + N)
+        bias = torch.randn(N, generator=torch.Generator().manual_seed(N)).to(dt).cuda()
+        xc, wc = x.cuda(), w.cuda()
+        want = bi.batch_invariant_matmul(xc, wc.T) + bias
+        for path in ("auto", "split", "fused", "fold"):
+            assert R.bits_of(bi.batch_invariant_matmul(xc, wc.T, bias=bias, path=path)) == R.bits_of(want), (M, N, K, path)
+    lin = torch.nn.Linear(1024, 384, device="cuda", dtype=dt)
+    xin = torch.randn(5, 1024, device="cuda", dtype=dt)
+    bi.reset_stats()
+    with bi.set_batch_invariant_mode(strict=True):
+        y = lin(xin)
+    assert bi.stats()["handled"] == {"addmm": 1}
+    assert R.bits_of(y) == R.bits_of(bi.batch_invariant_matmul(xin, lin.weight.T) + lin.bias)
+    bi.reset_stats()
+    bi.check_device_status()

@@ -81,3 +81,35 @@ def test_add_rms_norm_equals_add_then_norm(bi, dt, rows, D):
     _lib.check(_lib.load().bi_add_rms_norm(xg.data_ptr(), dg.data_ptr(), wg.data_ptr(), xg.data_ptr(), out.data_ptr(), rows, D,
                                            1e-5, _lib.DTYPE_CODE[dt], _lib.stream_ptr(xg.device)))
     assert R.bits_of(xg) == R.bits_of(s_ref) and R.bits_of(out) == R.bits_of(h)
+
+
+# ---- LayerNorm (the reference's roadmap item; same per-row scheme as RMSNorm) ---------------------------------
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,D", [(1, 4096), (5, 768), (3, 100), (2, 8192), (7, 33)])
+def test_layer_norm_bit_exact_vs_oracle(bi, dt, rows, D):
+    import mlx_batch_invariant_b200 as m
+    g = torch.Generator().manual_seed(rows * 1000 + D)
+    x = (3 * torch.randn(rows, D, generator=g) + 0.5).to(dt)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dt)
+    b = (0.1 * torch.randn(D, generator=g)).to(dt)
+    for ww, bb in ((w, b), (w, None), (None, None)):
+        got = m.batch_invariant_layer_norm(x.cuda(), None if ww is None else ww.cuda(), None if bb is None else bb.cuda(), 1e-5)
+        assert R.bits_of(got) == R.bits_of(R.layer_norm(x, ww, bb, 1e-5))
+    tol = 1e-5 if dt == torch.float32 else 2e-2
+    assert R.rel_err(R.layer_norm_f64(x, w, b, 1e-5), m.batch_invariant_layer_norm(x.cuda(), w.cuda(), b.cuda(), 1e-5)) < tol
+
+
+def test_layer_norm_rows_are_batch_invariant_and_routed_by_the_mode(bi):
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(256, 4096, generator=g).to(torch.bfloat16).cuda()
+    ln = torch.nn.LayerNorm(4096, device="cuda", dtype=torch.bfloat16)
+    bi.reset_stats()
+    with bi.set_batch_invariant_mode(strict=True):
+        full = ln(x)
+        for M in (1, 4, 16, 64):
+            assert R.bits_of(ln(x[:M])) == R.bits_of(full[:M])
+        assert R.bits_of(F.layer_norm(x[255:], (4096,), ln.weight, ln.bias, ln.eps)) == R.bits_of(full[255:])
+    assert bi.stats()["handled"]["layer_norm"] == 6 and bi.stats()["fallbacks"] == {}
+    bi.reset_stats()
