@@ -171,6 +171,18 @@ int bi_attn_decode_static(const void* q, const void* k, const void* v, void* out
                           int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t D, int64_t kv_sb, int64_t kv_sh,
                           int64_t kv_sl, float scale, int split_size, int dtype, void* stream);
 
+/* Decode attention over a PAGED cache: k_pages, v_pages are pools [pages, Hkv, page_size, D] (element strides
+ * pg_sp, pg_sh, pg_sl; unit stride along D), block_table[b * table_stride + i] names the page that holds keys
+ * [i * page_size, (i + 1) * page_size) of sequence b, kv_lens[b] its key count (<= max_pages * page_size).
+ * page_size: a multiple of 32 that divides the split size (or a multiple of it). 16-bit dtypes, D = 128.
+ * Same arithmetic as bi_attn_decode -- only where a key's row is found differs -- so the same bits as the same
+ * keys laid out contiguously. The reference reads one contiguous cache (it lists paged caches as future work,
+ * README.md:261-263); workspace as bi_attn_decode_workspace_bytes(B, Hq, max_pages * page_size, D, split_size). */
+int bi_attn_decode_paged(const void* q, const void* k_pages, const void* v_pages, void* out, const int32_t* kv_lens,
+                         const int32_t* block_table, void* workspace, size_t workspace_bytes, int64_t B, int64_t Hq,
+                         int64_t Hkv, int64_t max_pages, int64_t page_size, int64_t D, int64_t pg_sp, int64_t pg_sh,
+                         int64_t pg_sl, int64_t table_stride, float scale, int split_size, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Prefill attention (any number of queries, right-aligned to the cache end  *
  * when causal). replaces batch_invariant_prefill_attention /                *

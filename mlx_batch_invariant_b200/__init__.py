@@ -18,6 +18,7 @@ from .kernels import (
     batch_invariant_quantized_matmul,
     batch_invariant_rms_norm,
 )
+from .kernels import batch_invariant_paged_decode_attention  # extension (paged KV cache)
 from .kernels import batch_invariant_layer_norm  # extension (the reference's roadmap item); __all__ stays the reference's
 from ._lib import KernelError, check_device_status
 

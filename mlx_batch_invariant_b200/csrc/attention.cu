@@ -105,7 +105,11 @@ __device__ __forceinline__ float merge_acc(float A, float c_old, float acc, floa
 }
 
 struct KvLayout {
-    int64_t sb, sh, sl;  // element strides of k and v: batch, kv head, key
+    int64_t sb, sh, sl;  // element strides of k and v: batch (or page, when paged), kv head, key
+    // Paged cache (table != nullptr): k and v are pools of pages [page, kv head, key in page, D]; keys
+    // [i * page_size, (i + 1) * page_size) of sequence b live in page table[b * table_stride + i].
+    const int32_t* table;
+    int page_size, table_stride;
 };
 
 // ---- decode: unit = (batch, kv head, chunk of GU query heads, split) ----------
@@ -693,14 +697,24 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
         const T* const kb = k + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
         const T* const vb = v + (int64_t)b * lay.sb + (int64_t)hk * lay.sh + (int64_t)j0 * lay.sl;
         const int nblk = (nk + KL_KEYS - 1) / KL_KEYS;
+        // first row of key block `blk` of the split: contiguous cache, or the page that holds it (a page is a
+        // multiple of 32 keys, so a block never straddles two)
+        auto block_rows = [&](const T* pool, const T* contiguous, int blk) -> const T* {
+            if (lay.table == nullptr) return contiguous + (int64_t)blk * KL_KEYS * lay.sl;
+            const int key = j0 + blk * KL_KEYS;
+            const int page = lay.table[(int64_t)b * lay.table_stride + key / lay.page_size];
+            return pool + (int64_t)page * lay.sb + (int64_t)hk * lay.sh + (int64_t)(key % lay.page_size) * lay.sl;
+        };
 
         // a block of 32 rows: 512 pieces of 16 bytes, 16 per lane, consecutive lanes on consecutive pieces
         // lane's first piece of a block: row (lane >> 4), segment (lane & 15); each further piece is two rows on
         const int64_t row_bytes = lay.sl * (int64_t)sizeof(T);
-        auto issue_rows = [&](const T* src, uint32_t dst, int pitch, int blk) {
-            const int r0 = blk * KL_KEYS + (lane >> 4);
+        auto issue_rows = [&](const T* pool, const T* contiguous, uint32_t dst, int pitch, int blk) {
+            const T* src = block_rows(pool, contiguous, blk);                   // row 0 of the block
+            const int r0 = lane >> 4;
+            const int last = nk - 1 - blk * KL_KEYS;                            // last valid row of the block
             const uint32_t d0 = dst + (lane >> 4) * pitch + (lane & 15) * 16;
-            if (blk * KL_KEYS + KL_KEYS <= nk) {
+            if (last >= KL_KEYS - 1) {
                 const uint8_t* g = reinterpret_cast<const uint8_t*>(src) + r0 * row_bytes + (lane & 15) * 16;
 #pragma unroll
                 for (int it = 0; it < 16; ++it)
@@ -708,14 +722,14 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
             } else {
 #pragma unroll
                 for (int it = 0; it < 16; ++it) {
-                    const int64_t row = min(r0 + it * 2, nk - 1);                                 // past the end: re-read a valid row
+                    const int64_t row = min(r0 + it * 2, last);                                   // past the end: re-read a valid row
                     const uint8_t* g = reinterpret_cast<const uint8_t*>(src) + row * row_bytes + (lane & 15) * 16;
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + it * 2 * pitch), "l"(g) : "memory");
                 }
             }
         };
         __syncwarp();                                                        // the previous item's reads are done
-        issue_rows(kb, kbuf_s, C::KPITCH, 0);
+        issue_rows(k, kb, kbuf_s, C::KPITCH, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
         // scaled queries as packed pairs: pair (8i + d, 8i + 4 + d) at qs[h][i][d]
 #pragma unroll
@@ -736,8 +750,8 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
             acc[h][0] = ptx::pack2(0.0f, 0.0f); acc[h][1] = ptx::pack2(0.0f, 0.0f);
         }
         for (int blk = 0; blk < nblk; ++blk) {
-            issue_rows(vb, vbuf_s, C::ROWB, blk);                            // lands while the scores are computed
-            if (KL_KBUFS == 2 && blk + 1 < nblk) issue_rows(kb, kbuf_s + ((blk + 1) & 1) * C::KBUF, C::KPITCH, blk + 1);
+            issue_rows(v, vb, vbuf_s, C::ROWB, blk);                         // lands while the scores are computed
+            if (KL_KBUFS == 2 && blk + 1 < nblk) issue_rows(k, kb, kbuf_s + ((blk + 1) & 1) * C::KBUF, C::KPITCH, blk + 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 1;" ::: "memory");            // this block's K rows have landed
             __syncwarp();
@@ -770,7 +784,7 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
                 asm volatile("cp.async.wait_group 0;" ::: "memory");        // V rows (and the next K rows) have landed
             } else {
                 __syncwarp();                                                // every lane has read its K row
-                if (blk + 1 < nblk) issue_rows(kb, kbuf_s, C::KPITCH, blk + 1);  // lands while this block is accumulated
+                if (blk + 1 < nblk) issue_rows(k, kb, kbuf_s, C::KPITCH, blk + 1);  // lands while this block is accumulated
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 asm volatile("cp.async.wait_group 1;" ::: "memory");        // this block's V rows have landed
             }
@@ -1050,6 +1064,8 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
                 return check_launch("bi_attn_decode combine");
             }
         }
+        if (lay.table != nullptr)
+            return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode_paged: needs 16-byte aligned rows and an even number of (sequence, head, split) partials");
         const int nchunk4 = (G + 3) / 4;
         const int64_t streams = B * Hkv * nchunk4 * nsplit;
         if (rows16 && streams < sms * 24) {
@@ -1120,6 +1136,8 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             return check_launch("bi_attn_decode combine");
         }
     }
+    if (lay.table != nullptr)
+        return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode_paged: paged caches are read by the 16-bit head_dim-128 kernel only");
 #define BI_DECODE_LAUNCH(GUV)                                                                              \
     decode_kernel<T, DL, GUV><<<grid, block, 0, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
                                                       (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk)
@@ -1216,4 +1234,29 @@ extern "C" int bi_attn_prefill(const void* q, const void* k, const void* v, void
     if (causal && Tq > L) return fail(BI_ERR_BAD_ARG, "bi_attn_prefill: causal needs Tq <= L (Tq=%lld L=%lld)", (long long)Tq, (long long)L);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     BI_DISPATCH_T_DL(launch_prefill, q, k, v, out, B, Hq, Hkv, Tq, L, lay, scale, causal, split_size, st);
+}
+
+extern "C" int bi_attn_decode_paged(const void* q, const void* k_pages, const void* v_pages, void* out, const int32_t* kv_lens,
+                                    const int32_t* block_table, void* workspace, size_t workspace_bytes, int64_t B, int64_t Hq,
+                                    int64_t Hkv, int64_t max_pages, int64_t page_size, int64_t D, int64_t pg_sp, int64_t pg_sh,
+                                    int64_t pg_sl, int64_t table_stride, float scale, int split_size, int dtype, void* stream) {
+    using namespace bi;
+    if (!block_table || !kv_lens) return fail(BI_ERR_BAD_ARG, "bi_attn_decode_paged: block_table and kv_lens are required");
+    if (page_size <= 0 || page_size % 32 != 0 || split_size % page_size != 0 && page_size % split_size != 0 || max_pages <= 0 ||
+        table_stride < max_pages)
+        return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode_paged: page_size %lld must be a multiple of 32 that divides, or is a multiple of, the split size %d",
+                    (long long)page_size, split_size);
+    if (dtype == BI_F32 || D != 128) return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode_paged: 16-bit caches with head_dim 128 only");
+    const int64_t L = max_pages * page_size;
+    KvLayout lay{pg_sp, pg_sh, pg_sl, block_table, (int)page_size, (int)table_stride};
+    int rc = check_common("bi_attn_decode_paged", q, k_pages, v_pages, out, B, Hq, Hkv, 1, L, D, lay, split_size, dtype);
+    if (rc || B == 0) return rc;
+    const size_t need = bi_attn_decode_workspace_bytes(B, Hq, L, D, split_size);
+    if (!workspace || workspace_bytes < need)
+        return fail(BI_ERR_WORKSPACE, "bi_attn_decode_paged: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if (!aligned(workspace, 16)) return fail(BI_ERR_MISALIGNED, "bi_attn_decode_paged: workspace must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* ws = static_cast<float*>(workspace);
+    if (dtype == BI_F16) return launch_decode<__half, 4>(q, k_pages, v_pages, out, kv_lens, ws, B, Hq, Hkv, L, lay, scale, split_size, st);
+    return launch_decode<__nv_bfloat16, 4>(q, k_pages, v_pages, out, kv_lens, ws, B, Hq, Hkv, L, lay, scale, split_size, st);
 }

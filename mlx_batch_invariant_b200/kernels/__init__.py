@@ -9,6 +9,7 @@ from .matmul import batch_invariant_matmul
 from .rmsnorm import batch_invariant_rms_norm
 from .layernorm import batch_invariant_layer_norm  # beyond the reference's six kernels: not in __all__
 from .quantized import batch_invariant_quantized_matmul
+from .attention import batch_invariant_paged_decode_attention  # beyond the reference's six kernels: not in __all__
 from .attention import (
     batch_invariant_attention,
     batch_invariant_decode_attention,

@@ -89,6 +89,34 @@ def batch_invariant_decode_attention(q, k, v, *, scale: float, split_size: int =
     return give_back(out, q, foreign)
 
 
+def batch_invariant_paged_decode_attention(q, k_pages, v_pages, block_table, kv_lens, *, scale: float,
+                                           split_size: int = SPLIT_SIZE):
+    """Decode attention over a paged cache (an extension; the reference reads one contiguous cache).
+    ``k_pages`` / ``v_pages``: [pages, Hkv, page_size, D]; ``block_table`` int32 [B, max_pages] names the pages of
+    every sequence in order; ``kv_lens`` int32 [B]. Same bits as the same keys in a contiguous cache."""
+    assert q.shape[2] == 1 and q.shape[3] == 128
+    qt, kt, vt, dev, foreign = _prep(q, k_pages, v_pages)
+    B, Hq, _, D = qt.shape
+    _, Hkv, page, _ = kt.shape
+    code = dtype_code(qt.dtype)
+    qc = qt.contiguous()
+    kt, vt, sp, sh, sl = _kv_layout(kt, vt)
+    table = adopt(block_table)[0].to(device=dev, dtype=torch.int32).contiguous()
+    lens = adopt(kv_lens)[0].to(device=dev, dtype=torch.int32).contiguous()
+    if table.ndim != 2 or table.shape[0] != B or lens.shape != (B,):
+        raise ValueError("block_table must be [B, max_pages] and kv_lens [B]")
+    max_pages = table.shape[1]
+    out = torch.empty_like(qc)
+    lib = _lib.load()
+    nbytes = lib.bi_attn_decode_workspace_bytes(B, Hq, max_pages * page, D, split_size)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.bi_attn_decode_paged(qc.data_ptr(), kt.data_ptr(), vt.data_ptr(), out.data_ptr(), lens.data_ptr(),
+                                            table.data_ptr(), ws.data_ptr(), nbytes, B, Hq, Hkv, max_pages, page, D, sp, sh, sl,
+                                            table.stride(0), float(scale), int(split_size), code, _lib.stream_ptr(dev)))
+    return give_back(out, q, foreign)
+
+
 def batch_invariant_prefill_attention(q, k, v, *, scale: float, causal: bool, split_size: int = SPLIT_SIZE):
     """Any T_q. Queries are right-aligned to the cache end when causal; same split loop and merge as decode."""
     assert q.shape[3] % 32 == 0

@@ -144,3 +144,29 @@ def test_golden_fixture(bi, name):
     assert make_golden.raw(pre).tobytes() == gold[f"{name}_prefill"].tobytes()
     dec = bi.batch_invariant_decode_attention(q[:, :, -1:], k, v, scale=0.125, kv_lens=torch.tensor([265, 100]))
     assert make_golden.raw(dec).tobytes() == gold[f"{name}_decode"].tobytes()
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("page", [32, 64, 256])
+def test_paged_cache_gives_the_bits_of_the_contiguous_cache(bi, dt, page):
+    """The same keys scattered over a shuffled page pool, found through a block table, give the bits of the
+    contiguous cache (and of the oracle): only the address of a key's row differs."""
+    import mlx_batch_invariant_b200 as m
+    B, Hq, Hkv, D = 5, 8, 2, 128
+    lens = [1, 255, 257, 600, 700]
+    cap = 768
+    q, k, v = qkv(B, Hq, Hkv, 1, cap, D, dt, page)
+    want = R.attn_decode(q, k, v, scale=D ** -0.5, kv_lens=lens)
+    per_seq = cap // page
+    g = torch.Generator().manual_seed(7)
+    perm = torch.randperm(B * per_seq + 3, generator=g)[:B * per_seq].reshape(B, per_seq).to(torch.int32)
+    kp = torch.zeros(B * per_seq + 3, Hkv, page, D, dtype=dt)
+    vp = torch.zeros_like(kp)
+    for b in range(B):
+        for i in range(per_seq):
+            kp[perm[b, i]] = k[b, :, i * page:(i + 1) * page]
+            vp[perm[b, i]] = v[b, :, i * page:(i + 1) * page]
+    got = m.batch_invariant_paged_decode_attention(q.cuda(), kp.cuda(), vp.cuda(), perm.cuda(), torch.tensor(lens), scale=D ** -0.5)
+    assert R.bits_of(got) == R.bits_of(want)
+    flat = bi.batch_invariant_decode_attention(q.cuda(), k.cuda(), v.cuda(), scale=D ** -0.5, kv_lens=torch.tensor(lens))
+    assert R.bits_of(got) == R.bits_of(flat)
