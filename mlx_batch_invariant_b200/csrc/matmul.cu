@@ -25,7 +25,7 @@ TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
     TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO, Await{nullptr, nullptr, 0, 0}, nullptr};
     const int64_t G = ngroups(K);
     const int64_t nt = (N + 127) / 128;
-    const int64_t fill = (int64_t)sm_count() * 4 / 5;
+    const int64_t fill = (int64_t)sm_count() * 3 / 4;
     int bm_fill = 0;                               // tallest batch tile that still fills the GPU
     for (int bm = 128; bm >= 16; bm >>= 1)
         if (nt * ((M + bm - 1) / bm) >= fill) { bm_fill = bm; break; }
@@ -67,7 +67,7 @@ int tc_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int64
     if (pa.kind == BI_MATMUL_FUSED && sh->split) {
         sh->split = false;
         sh->bm = 128;
-        const int64_t nt = (N + 127) / 128, fill = (int64_t)sm_count() * 4 / 5;
+        const int64_t nt = (N + 127) / 128, fill = (int64_t)sm_count() * 3 / 4;
         while (sh->bm > 16 && nt * ((M + sh->bm - 1) / sh->bm) < fill) sh->bm >>= 1;
     }
     if (pa.bm) sh->bm = pa.bm;
