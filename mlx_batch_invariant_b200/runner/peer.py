@@ -28,6 +28,10 @@ def pick_cycle(n: int, mod: int, calls: int) -> tuple[int, int]:
     The buffer of call c is c % modulus. The modulus is the smallest of 3, 4, 5, 7 for which the last gather of
     one replay and the first of the next use different buffers (n % modulus != 1), and the counter is
     re-based so that the first gather of the sequence does not reuse the buffer of the gather before it."""
+    if n == 1:
+        raise RuntimeError("a replayed sequence of ONE gather would reuse one destination buffer every replay, which a "
+                           "peer that is one gather ahead may still be writing: capture at least two gathers per replay, "
+                           "or run the step eagerly")
     prev = (calls - 1) % mod if calls else -1
     for m in (3, 4, 5, 7):
         if n % m != 1:
@@ -74,7 +78,12 @@ class PushGather:
         return rows * row_bytes * self.world <= self.cap and row_bytes % 16 == 0
 
     def set_cycle(self, n: int) -> None:
-        """A sequence of n gathers is about to be replayed back to back: pick the rotation modulus."""
+        """A sequence of n gathers is about to be replayed back to back: pick the rotation modulus. One captured
+        sequence per PushGather: capturing a second one re-bases the rotation under the graph already recorded,
+        so build a new PushGather (a new ShardedDecoder) for a second graph."""
+        if getattr(self, "_cycle_set", False):
+            raise RuntimeError("this PushGather already serves a captured sequence of gathers; a second capture needs its own")
+        self._cycle_set = True
         self.mod, self.calls = pick_cycle(n, self.mod, self.calls)
 
     def _slot(self):

@@ -49,6 +49,7 @@ def compute() -> dict:
     for name, dt in DT.items():
         i = inputs(name)
         out[f"{name}_rms"] = raw(R.rms_norm(i["rms_x"], i["rms_w"], 1e-5))
+        out[f"{name}_ln"] = raw(R.layer_norm(i["rms_x"], i["rms_w"], i["rms_w"] - 1, 1e-5))
         out[f"{name}_prefill"] = raw(R.attn_prefill(i["q"], i["k"], i["v"], scale=0.125, causal=True))
         out[f"{name}_decode"] = raw(R.attn_decode(i["q"][:, :, -1:], i["k"], i["v"], scale=0.125, kv_lens=[265, 100]))
         out[f"{name}_mm"] = raw(R.matmul_f32order(i["a"], i["w"].T.contiguous()))

@@ -43,6 +43,8 @@ def test_golden_fixture(bi, name):
     i = make_golden.inputs(name)
     got = bi.batch_invariant_rms_norm(i["rms_x"].cuda(), i["rms_w"].cuda(), 1e-5)
     assert make_golden.raw(got).tobytes() == gold[f"{name}_rms"].tobytes()
+    ln = bi.batch_invariant_layer_norm(i["rms_x"].cuda(), i["rms_w"].cuda(), (i["rms_w"] - 1).cuda(), 1e-5)
+    assert make_golden.raw(ln).tobytes() == gold[f"{name}_ln"].tobytes()
 
 
 @pytest.mark.parametrize("dt", DTS)
