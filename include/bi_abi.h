@@ -280,6 +280,31 @@ int bi_add_rms_norm_awaiting(const void* x, const void* delta, const void* w, vo
                              int64_t D, float eps, int dtype, void* stream, const uint32_t* flags,
                              const uint32_t* epoch, int rank, int world, int32_t* status);
 
+/* Producer-side fusion: the kernel that finishes an op's output IS the gather. bi_matmul_push / bi_qmm_push are
+ * bi_matmul / bi_qmm (tensor-core weights only; always the split launch shape, so the workspace must hold
+ * ceil(K/256) * M * N * 4 bytes, + BI_MATMUL_COUNTER_BYTES with BI_MATMUL_WS_ZEROED) whose fold kernel stores
+ * out[m, n] into column rank * N + n of every rank's [M, world * N] destination and ends with the push gather's
+ * handshake; bi_attn_decode_push is bi_attn_decode whose split merge stores (b, h, d) into column
+ * rank * Hq * D + h * D + d of every rank's [B, world * Hq * D] destination. dst / peer_flags / counters / wait /
+ * status as in bi_push_gather (same protocol state, same epochs: the calls can be mixed with bi_push_gather on
+ * one stream). await_flags / await_epoch (NULL: none): the activation is itself a gathered buffer nobody has
+ * waited for yet, as in bi_matmul_awaiting. Same bits as the plain op followed by bi_push_gather. No counterpart
+ * in the reference (single device). */
+int bi_matmul_push(const void* a, const void* b, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                   int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, int path,
+                   int32_t* status, void* stream, const uint32_t* await_flags, const uint32_t* await_epoch,
+                   void* const* dst, void* const* peer_flags, uint32_t* counters, int rank, int world, int wait);
+int bi_qmm_push(const void* x, const uint32_t* w, const void* scales, const void* biases, void* workspace,
+                size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm, int group_size, int bits,
+                int dtype, int path, int32_t* status, void* stream, const uint32_t* await_flags,
+                const uint32_t* await_epoch, void* const* dst, void* const* peer_flags, uint32_t* counters, int rank,
+                int world, int wait);
+int bi_attn_decode_push(const void* q, const void* k, const void* v, const int32_t* kv_lens, void* workspace,
+                        size_t workspace_bytes, int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t D,
+                        int64_t kv_sb, int64_t kv_sh, int64_t kv_sl, float scale, int split_size, int dtype,
+                        void* stream, void* const* dst, void* const* peer_flags, uint32_t* counters, int rank,
+                        int world, int wait, int32_t* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,7 @@
 #include <algorithm>
 #include "bi_common.cuh"
 #include "bi_ptx.cuh"
+#include "peer_push.cuh"
 
 namespace bi {
 namespace {
@@ -823,26 +824,49 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
 }
 
 
-template <typename T>
+// PUSH: the merged output is this rank's head slice of a gathered activation [B, world * Hq * D]: element (b, h, d)
+// goes to column rank * Hq * D + h * D + d of every rank's destination and the launch ends with the gather's
+// handshake (peer_push.cuh): the split merge and the all-gather after it are one kernel.
+template <typename T, bool PUSH>
 __global__ void __launch_bounds__(256) decode_combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                                                              const float* __restrict__ pacc,
                                                              const int32_t* __restrict__ kv_lens, T* __restrict__ out,
-                                                             int64_t BH, int Hq, int D, int L, int split, int nsplit) {
+                                                             int64_t BH, int Hq, int D, int L, int split, int nsplit,
+                                                             PushSink sink) {
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= BH * D) return;
-    const int64_t bh = gid / D;
-    const int d = (int)(gid % D);
-    const int b = (int)(bh / Hq);
-    const int Lb = kv_lens ? min(kv_lens[b], L) : L;
-    const int ns = (Lb + split - 1) / split;
-    float M = -INFINITY, Ls = 0.0f, A = 0.0f;
-    for (int i = 0; i < ns; ++i) {
-        const int64_t po = bh * nsplit + i;
-        float c_old, c_new;
-        merge_coeffs(M, Ls, pm[po], pl[po], c_old, c_new);
-        A = merge_acc(A, c_old, pacc[po * D + d], c_new);
+    if (gid < BH * D) {
+        const int64_t bh = gid / D;
+        const int d = (int)(gid % D);
+        const int b = (int)(bh / Hq);
+        const int Lb = kv_lens ? min(kv_lens[b], L) : L;
+        const int ns = (Lb + split - 1) / split;
+        float M = -INFINITY, Ls = 0.0f, A = 0.0f;
+        for (int i = 0; i < ns; ++i) {
+            const int64_t po = bh * nsplit + i;
+            float c_old, c_new;
+            merge_coeffs(M, Ls, pm[po], pl[po], c_old, c_new);
+            A = merge_acc(A, c_old, pacc[po * D + d], c_new);
+        }
+        const T val = Cvt<T>::down(div_canon(A, Ls));
+        if (PUSH) {
+            const int64_t f = (int64_t)Hq * D;
+            const int64_t o = (int64_t)b * f * sink.world + (int64_t)sink.rank * f + (gid - (int64_t)b * f);
+            for (int r = 0; r < sink.world; ++r) static_cast<T*>(sink.dst.p[r])[o] = val;
+        } else {
+            out[bh * D + d] = val;
+        }
     }
-    out[bh * D + d] = Cvt<T>::down(div_canon(A, Ls));
+    if (PUSH) push_handshake(sink);
+}
+
+template <typename T>
+int launch_decode_combine(const float* pm, const float* pl, const float* pacc, const int32_t* kv_lens, void* out, int64_t BH,
+                          int Hq, int D, int L, int split, int nsplit, const PushSink* sink, cudaStream_t st) {
+    const int64_t n = BH * D;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (sink) decode_combine_kernel<T, true><<<blocks, 256, 0, st>>>(pm, pl, pacc, kv_lens, nullptr, BH, Hq, D, L, split, nsplit, *sink);
+    else decode_combine_kernel<T, false><<<blocks, 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, Hq, D, L, split, nsplit, PushSink{});
+    return check_launch("bi_attn_decode combine");
 }
 
 // ---- prefill: unit = (batch, head, block of QB consecutive queries) -----------
@@ -1000,7 +1024,7 @@ int check_common(const char* op, const void* q, const void* k, const void* v, co
 template <typename T, int DL>
 int launch_decode(const void* q, const void* k, const void* v, void* out, const int32_t* kv_lens, float* ws,
                   int64_t B, int64_t Hq, int64_t Hkv, int64_t L, const KvLayout& lay, float scale, int split,
-                  cudaStream_t st) {
+                  cudaStream_t st, const PushSink* sink = nullptr) {
     constexpr int D = 32 * DL;
     const int G = (int)(Hq / Hkv);
     const int nsplit = (int)((L + split - 1) / split);
@@ -1060,8 +1084,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
                 int rck = check_launch("bi_attn_decode (key per lane)");
                 if (rck) return rck;
                 const int64_t n2k = BH * D;
-                decode_combine_kernel<T><<<(unsigned)((n2k + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
-                return check_launch("bi_attn_decode combine");
+                return launch_decode_combine<T>(pm, pl, pacc, kv_lens, out, BH, (int)Hq, D, (int)L, split, nsplit, sink, st);
             }
         }
         if (lay.table != nullptr)
@@ -1111,8 +1134,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             int rcw = check_launch("bi_attn_decode (warp per stream)");
             if (rcw) return rcw;
             const int64_t n2w = BH * D;
-            decode_combine_kernel<T><<<(unsigned)((n2w + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
-            return check_launch("bi_attn_decode combine");
+            return launch_decode_combine<T>(pm, pl, pacc, kv_lens, out, BH, (int)Hq, D, (int)L, split, nsplit, sink, st);
         }
         if (rows16) {
             using C = Dec2Cfg<T, DL>;
@@ -1132,8 +1154,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             int rc2 = check_launch("bi_attn_decode (streamed)");
             if (rc2) return rc2;
             const int64_t n2s = BH * D;
-            decode_combine_kernel<T><<<(unsigned)((n2s + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
-            return check_launch("bi_attn_decode combine");
+            return launch_decode_combine<T>(pm, pl, pacc, kv_lens, out, BH, (int)Hq, D, (int)L, split, nsplit, sink, st);
         }
     }
     if (lay.table != nullptr)
@@ -1152,8 +1173,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
     int rc = check_launch("bi_attn_decode");
     if (rc) return rc;
     const int64_t n2 = BH * D;
-    decode_combine_kernel<T><<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, (int)Hq, D, (int)L, split, nsplit);
-    return check_launch("bi_attn_decode combine");
+    return launch_decode_combine<T>(pm, pl, pacc, kv_lens, out, BH, (int)Hq, D, (int)L, split, nsplit, sink, st);
 }
 
 template <typename T, int DL>
@@ -1222,6 +1242,31 @@ extern "C" int bi_attn_decode(const void* q, const void* k, const void* v, void*
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float* ws = static_cast<float*>(workspace);
     BI_DISPATCH_T_DL(launch_decode, q, k, v, out, kv_lens, ws, B, Hq, Hkv, L, lay, scale, split_size, st);
+}
+
+// bi_attn_decode whose merged output is pushed, as this rank's head slice, into every rank's gathered activation
+// [B, world * Hq * D] (the split merge is the gather kernel; see peer_push.cuh for the handshake).
+extern "C" int bi_attn_decode_push(const void* q, const void* k, const void* v, const int32_t* kv_lens, void* workspace,
+                                   size_t workspace_bytes, int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t D,
+                                   int64_t kv_sb, int64_t kv_sh, int64_t kv_sl, float scale, int split_size, int dtype,
+                                   void* stream, void* const* dst, void* const* peer_flags, uint32_t* counters, int rank,
+                                   int world, int wait, int32_t* status) {
+    using namespace bi;
+    KvLayout lay{kv_sb, kv_sh, kv_sl};
+    PushSink sink;
+    int rc = make_sink("bi_attn_decode_push", dst, peer_flags, counters, rank, world, wait, status, dtype_ok(dtype) ? dtype_size(dtype) : 1, &sink);
+    if (rc) return rc;
+    rc = check_common("bi_attn_decode_push", q, k, v, dst[rank], B, Hq, Hkv, 1, L, D, lay, split_size, dtype);
+    if (rc || B == 0) return rc;
+    const size_t need = bi_attn_decode_workspace_bytes(B, Hq, L, D, split_size);
+    if (!workspace || workspace_bytes < need)
+        return fail(BI_ERR_WORKSPACE, "bi_attn_decode_push: workspace %zu bytes, need %zu", workspace_bytes, need);
+    if (!aligned(workspace, 16)) return fail(BI_ERR_MISALIGNED, "bi_attn_decode_push: workspace must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* ws = static_cast<float*>(workspace);
+    const PushSink* sp = &sink;
+    void* out = nullptr;
+    BI_DISPATCH_T_DL(launch_decode, q, k, v, out, kv_lens, ws, B, Hq, Hkv, L, lay, scale, split_size, st, sp);
 }
 
 extern "C" int bi_attn_prefill(const void* q, const void* k, const void* v, void* out, int64_t B, int64_t Hq,

@@ -133,11 +133,12 @@ int check_await(const char* op, const Await& aw) {
 
 int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
                 int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
-                int path, int32_t* status, void* stream, const Await& aw, const void* bias = nullptr) {
+                int path, int32_t* status, void* stream, const Await& aw, const void* bias = nullptr,
+                const PushSink* sink = nullptr) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dtype %d", dtype);
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_matmul: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return BI_OK;
-    if (!a || !b || !out) return fail(BI_ERR_BAD_ARG, "bi_matmul: null pointer");
+    if (!a || !b || (!out && !sink)) return fail(BI_ERR_BAD_ARG, "bi_matmul: null pointer");
     if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dimension too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t es = dtype_size(dtype);
@@ -149,6 +150,10 @@ int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t
     PathArg pa;
     int rc = parse_path("bi_matmul", path, &pa);
     if (rc) return rc;
+    if (sink) {      // the fold kernel is the one that pushes: always the split shape, folded by the second launch
+        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_push: only weights on the tensor-core path can push their output");
+        pa.kind = BI_MATMUL_SPLIT;
+    }
     float* part = nullptr;
     if (weight_tc) {
         const int64_t x_ld = M == 1 ? K : a_sm;
@@ -162,7 +167,7 @@ int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t
         const int64_t w_ld = N == 1 ? K : b_sn;
         rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
-        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, bias, N);
+        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, bias, N, sink);
     }
     if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_awaiting: only weights on the tensor-core path can wait for a gather");
     bool split;
@@ -203,7 +208,8 @@ namespace bi {
 namespace {
 int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
              void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
-             int group_size, int bits, int dtype, int path, int32_t* status, void* stream, const Await& aw) {
+             int group_size, int bits, int dtype, int path, int32_t* status, void* stream, const Await& aw,
+             const PushSink* sink = nullptr) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: dtype %d", dtype);
     if (bits != 4 && bits != 8) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: bits=%d (supported: 4, 8)", bits);
     if (group_size != 32 && group_size != 64 && group_size != 128)
@@ -211,7 +217,7 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_qmm: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (K % group_size != 0) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
     if (M == 0 || N == 0) return BI_OK;
-    if (!x || !w || !scales || !biases || !out) return fail(BI_ERR_BAD_ARG, "bi_qmm: null pointer");
+    if (!x || !w || !scales || !biases || (!out && !sink)) return fail(BI_ERR_BAD_ARG, "bi_qmm: null pointer");
     if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: dimension too large");
     if (M > 1 && x_sm < K) return fail(BI_ERR_BAD_ARG, "bi_qmm: row stride %lld < K", (long long)x_sm);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -222,6 +228,10 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
     PathArg pa;
     int rc = parse_path("bi_qmm", path, &pa);
     if (rc) return rc;
+    if (sink) {
+        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_push: only weights on the tensor-core path can push their output");
+        pa.kind = BI_MATMUL_SPLIT;
+    }
     float* part = nullptr;
     if (weight_tc) {
         const int64_t x_ld = M == 1 ? K : x_sm;
@@ -233,7 +243,7 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
         sh.await = aw;
         rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
-        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st);
+        return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, nullptr, N, sink);
     }
     if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_awaiting: only weights on the tensor-core path can wait for a gather");
     bool split;
@@ -260,4 +270,36 @@ extern "C" int bi_qmm_awaiting(const void* x, const uint32_t* w, const void* sca
     if (rc) return rc;
     return bi::qmm_impl(x, w, scales, biases, out, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
                         stream, aw);
+}
+
+// ---- output pushed into every rank's gathered activation (the fold of the split shape is the gather kernel) ----
+extern "C" int bi_matmul_push(const void* a, const void* b, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                              int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, int path,
+                              int32_t* status, void* stream, const uint32_t* await_flags, const uint32_t* await_epoch,
+                              void* const* dst, void* const* peer_flags, uint32_t* counters, int rank, int world, int wait) {
+    using namespace bi;
+    const Await aw{await_flags, await_flags ? await_epoch : nullptr, await_flags ? rank : 0, await_flags ? world : 0};
+    int rc = check_await("bi_matmul_push", aw);
+    if (rc) return rc;
+    PushSink sink;
+    rc = make_sink("bi_matmul_push", dst, peer_flags, counters, rank, world, wait, status, dtype_ok(dtype) ? dtype_size(dtype) : 1, &sink);
+    if (rc) return rc;
+    return matmul_impl(a, b, nullptr, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream, aw,
+                       nullptr, &sink);
+}
+
+extern "C" int bi_qmm_push(const void* x, const uint32_t* w, const void* scales, const void* biases, void* workspace,
+                           size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm, int group_size, int bits,
+                           int dtype, int path, int32_t* status, void* stream, const uint32_t* await_flags,
+                           const uint32_t* await_epoch, void* const* dst, void* const* peer_flags, uint32_t* counters, int rank,
+                           int world, int wait) {
+    using namespace bi;
+    const Await aw{await_flags, await_flags ? await_epoch : nullptr, await_flags ? rank : 0, await_flags ? world : 0};
+    int rc = check_await("bi_qmm_push", aw);
+    if (rc) return rc;
+    PushSink sink;
+    rc = make_sink("bi_qmm_push", dst, peer_flags, counters, rank, world, wait, status, dtype_ok(dtype) ? dtype_size(dtype) : 1, &sink);
+    if (rc) return rc;
+    return qmm_impl(x, w, scales, biases, nullptr, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
+                    stream, aw, &sink);
 }

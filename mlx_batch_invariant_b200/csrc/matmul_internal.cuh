@@ -2,13 +2,16 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "peer_push.cuh"
 
 namespace bi {
 
 // Split-path fold: out[i] = T(((0 + part[0][i]) + part[1][i]) + ...), part is [G][MN] fp32.
 // bias: optional [N] in the output dtype (N = row length of out), added after the rounding.
+// sink: when given (N must then be the row length), `out` is ignored and the result is pushed as this rank's column
+// slice into every rank's gathered activation, handshake included.
 int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias = nullptr,
-                   int64_t N = 1);
+                   int64_t N = 1, const PushSink* sink = nullptr);
 
 // CUDA-core path (fp32 inputs, or weights TMA cannot address).
 int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,

@@ -133,41 +133,67 @@ __global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restric
 
 // out[idx] = T(((0 + p_0[idx]) + p_1[idx]) + ...): the fold of the split path
 // (reference: bi_matmul_combine, mlx_batch_invariant/kernels/matmul.py:226-234).
-template <typename T, int VEC>
+// PUSH: the output is this rank's column slice of a gathered activation: out[m, n] goes to column rank * N + n of
+// every rank's [M, world * N] destination, and the launch ends with the gather's handshake (peer_push.cuh) -- the
+// fold and the all-gather that follows it are one kernel, the local slice never exists in memory.
+template <typename T, int VEC, bool PUSH>
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ part, T* __restrict__ out, int G,
-                                                      int64_t MN, const T* __restrict__ bias, int64_t N) {
+                                                      int64_t MN, const T* __restrict__ bias, int64_t N, PushSink sink) {
     const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-    if (i0 >= MN) return;
-    float total[VEC];
+    if (i0 < MN) {
+        float total[VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) total[v] = 0.0f;
-    for (int g = 0; g < G; ++g) {
-        const float* p = part + (int64_t)g * MN + i0;
-        if (VEC == 4) {
-            const float4 x = *reinterpret_cast<const float4*>(p);
-            total[0] = add_rn(total[0], x.x); total[1 % VEC] = add_rn(total[1 % VEC], x.y);
-            total[2 % VEC] = add_rn(total[2 % VEC], x.z); total[3 % VEC] = add_rn(total[3 % VEC], x.w);
+        for (int v = 0; v < VEC; ++v) total[v] = 0.0f;
+        for (int g = 0; g < G; ++g) {
+            const float* p = part + (int64_t)g * MN + i0;
+            if (VEC == 4) {
+                const float4 x = *reinterpret_cast<const float4*>(p);
+                total[0] = add_rn(total[0], x.x); total[1 % VEC] = add_rn(total[1 % VEC], x.y);
+                total[2 % VEC] = add_rn(total[2 % VEC], x.z); total[3 % VEC] = add_rn(total[3 % VEC], x.w);
+            } else {
+                total[0] = add_rn(total[0], p[0]);
+            }
+        }
+        if (PUSH) {
+            // VEC consecutive outputs stay inside one row (N % VEC == 0 is checked by the launcher)
+            const int64_t m = i0 / N, n = i0 - m * N;
+            const int64_t o = m * N * sink.world + (int64_t)sink.rank * N + n;
+            T vals[VEC];
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) vals[v] = round_out<T>(total[v], bias, bias ? n + v : 0);
+            for (int r = 0; r < sink.world; ++r) {
+                T* d = static_cast<T*>(sink.dst.p[r]) + o;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) d[v] = vals[v];
+            }
         } else {
-            total[0] = add_rn(total[0], p[0]);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) out[i0 + v] = round_out<T>(total[v], bias, bias ? (i0 + v) % N : 0);
         }
     }
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) out[i0 + v] = round_out<T>(total[v], bias, bias ? (i0 + v) % N : 0);
+    if (PUSH) push_handshake(sink);
 }
 
 template <typename T>
-int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st, const void* bias_v, int64_t N) {
+int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st, const void* bias_v, int64_t N,
+              const PushSink* sink = nullptr) {
     const T* bias = static_cast<const T*>(bias_v);
-    if (MN % 4 == 0 && aligned(part, 16) && MN < (1 << 20)) {
+    const bool vec_ok = MN % 4 == 0 && aligned(part, 16) && (!sink || N % 4 == 0);
+    const PushSink none{};
+#define BI_COMBINE(VEC, THREADS_)                                                                                        \
+    do {                                                                                                                 \
+        const unsigned blocks_ = (unsigned)(((THREADS_) + 255) / 256);                                                  \
+        if (sink) combine_kernel<T, VEC, true><<<blocks_, 256, 0, st>>>(part, nullptr, G, MN, bias, N, *sink);          \
+        else combine_kernel<T, VEC, false><<<blocks_, 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N, none);  \
+    } while (0)
+    if (vec_ok && MN >= (1 << 20)) {
+        BI_COMBINE(4, MN / 4);
+    } else {
         // few outputs: one per thread, so that enough loads are in flight to cover the L2 latency
         // (4096x14336 at M = 16: 31.1 -> 28.3 us for matmul + combine)
-        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
-    } else if (MN % 4 == 0 && aligned(part, 16)) {
-        const int64_t threads = MN / 4;
-        combine_kernel<T, 4><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
-    } else {
-        combine_kernel<T, 1><<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N);
+        BI_COMBINE(1, MN);
     }
+#undef BI_COMBINE
     return check_launch("matmul combine");
 }
 
@@ -193,11 +219,12 @@ int simt_t(const void* a, const void* b, const QuantArgs& qa, void* out, float* 
 
 }  // namespace
 
-int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias, int64_t N) {
+int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias, int64_t N,
+                   const PushSink* sink) {
     switch (dtype) {
-        case BI_F32: return combine_t<float>(part, out, G, MN, st, bias, N);
-        case BI_F16: return combine_t<__half>(part, out, G, MN, st, bias, N);
-        default:     return combine_t<__nv_bfloat16>(part, out, G, MN, st, bias, N);
+        case BI_F32: return combine_t<float>(part, out, G, MN, st, bias, N, sink);
+        case BI_F16: return combine_t<__half>(part, out, G, MN, st, bias, N, sink);
+        default:     return combine_t<__nv_bfloat16>(part, out, G, MN, st, bias, N, sink);
     }
 }
 

@@ -21,55 +21,10 @@
 #include <cstring>
 #include "bi_common.cuh"
 #include "bi_ptx.cuh"
+#include "peer_push.cuh"
 
 namespace bi {
 namespace {
-
-constexpr int MAX_RANKS = 8;
-constexpr uint64_t GATHER_WAIT_NS = 2000000000ull;
-
-struct PeerPtrs {
-    void* p[MAX_RANKS];
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-    return v;
-}
-
-// After a CTA's stores: fence system-wide; the last CTA of the launch raises this rank's epoch flag at every peer and
-// waits (bounded) for theirs. counters[0]: CTAs of the current launch that have pushed their part; counters[1]: epoch
-// of the last gather.
-// wait == 0: raise the flags and return; whoever reads the gathered buffer waits for the peers' flags itself.
-__device__ __forceinline__ void push_handshake(int rank, int R, const PeerPtrs& flags, unsigned* counters, int32_t* status, int wait) {
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x != 0) return;
-    if (atomicAdd(&counters[0], 1u) != gridDim.x - 1) return;
-    // last CTA of this rank: every store of the launch has been fenced
-    atomicExch(&counters[0], 0u);
-    const uint32_t epoch = counters[1] + 1u;
-    counters[1] = epoch;
-    __threadfence_system();
-    for (int r = 0; r < R; ++r)
-        if (r != rank) st_release_sys(static_cast<uint32_t*>(flags.p[r]) + rank, epoch);
-    if (!wait) return;
-    const uint32_t* mine = static_cast<const uint32_t*>(flags.p[rank]);
-    const uint64_t t0 = ptx::globaltimer_ns();
-    for (int r = 0; r < R; ++r) {
-        if (r == rank) continue;
-        while ((int32_t)(ld_acquire_sys(mine + r) - epoch) < 0) {
-            if (ptx::globaltimer_ns() - t0 > GATHER_WAIT_NS) {
-                if (status) atomicCAS(status, 0, (int)(0x20000 | (r << 8) | (epoch & 0xff)));
-                return;
-            }
-        }
-    }
-}
 
 __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restrict__ local, long long rows, int f16, int rank,
                                                           int R, PeerPtrs dst, PeerPtrs flags, unsigned* counters,

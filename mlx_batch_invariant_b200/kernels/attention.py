@@ -64,8 +64,11 @@ def _kv_layout(k: torch.Tensor, v: torch.Tensor):
     return k, v, k.stride(0), k.stride(1), k.stride(2)
 
 
-def batch_invariant_decode_attention(q, k, v, *, scale: float, split_size: int = SPLIT_SIZE, kv_lens=None):
-    """T_q == 1. Per-split partials (query heads of a kv head share K/V rows), then an ordered combine."""
+def batch_invariant_decode_attention(q, k, v, *, scale: float, split_size: int = SPLIT_SIZE, kv_lens=None, push=None):
+    """T_q == 1. Per-split partials (query heads of a kv head share K/V rows), then an ordered combine.
+    ``push`` (``PushGather.sink()``): the output is this rank's head slice of a gathered [B, world * Hq * D]
+    activation; the combine kernel stores it into every rank's destination and shakes hands
+    (``bi_attn_decode_push``); nothing is returned."""
     assert q.shape[2] == 1 and q.shape[3] % 32 == 0
     qt, kt, vt, dev, foreign = _prep(q, k, v)
     B, Hq, Tq, D = qt.shape
@@ -78,10 +81,16 @@ def batch_invariant_decode_attention(q, k, v, *, scale: float, split_size: int =
         lens = adopt(kv_lens)[0].to(device=dev, dtype=torch.int32).contiguous()
         if lens.shape != (B,):
             raise ValueError(f"kv_lens must have shape ({B},), got {tuple(lens.shape)}")
-    out = torch.empty_like(qc)
     lib = _lib.load()
     nbytes = lib.bi_attn_decode_workspace_bytes(B, Hq, L, D, split_size)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+    if push is not None:
+        with torch.cuda.device(dev):
+            _lib.check(lib.bi_attn_decode_push(qc.data_ptr(), kt.data_ptr(), vt.data_ptr(), _lib.ptr(lens), ws.data_ptr(), nbytes,
+                                               B, Hq, Hkv, L, D, sb, sh, sl, float(scale), int(split_size), code,
+                                               _lib.stream_ptr(dev), *push, _lib.status_word(dev).data_ptr()))
+        return None
+    out = torch.empty_like(qc)
     with torch.cuda.device(dev):
         _lib.check(lib.bi_attn_decode(qc.data_ptr(), kt.data_ptr(), vt.data_ptr(), out.data_ptr(), _lib.ptr(lens),
                                       ws.data_ptr(), nbytes, B, Hq, Hkv, L, D, sb, sh, sl, float(scale),

@@ -39,7 +39,7 @@ def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
             and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
 
 
-def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None, bias=None):
+def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None, bias=None, push=None):
     """``a @ b`` with a batch-invariant reduction order.
 
     ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
@@ -49,6 +49,9 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
     that ``a`` is the destination of a peer gather nobody has waited for yet: the kernel waits for it itself,
     after it has started streaming the weight (runner/peer.py). ``bias`` ([N], the output dtype) is added to the
     rounded product in the kernel's epilogue: the bits of ``batch_invariant_matmul(a, b) + bias``.
+    ``push`` (destination table, flag table, counters pointer, rank, world, wait -- ``PushGather.sink()``): the
+    product is this rank's column slice of a gathered activation; the fold kernel stores it into every rank's
+    destination and shakes hands (``bi_matmul_push``); nothing is returned.
     """
     at, foreign = adopt(a)
     bt, _ = adopt(b)
@@ -74,8 +77,18 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
         return give_back(torch.zeros((*lead, N), dtype=out_dtype, device=dev), a, foreign)
     if M > 0 and _weight_is_tensor_core(bt, K):
         a2 = rows_16b(a2)
-    out = torch.empty((M, N), dtype=out_dtype, device=dev)
     lib = _lib.load()
+    if push is not None:
+        if bias is not None or M == 0:
+            raise ValueError("push cannot be combined with bias or an empty batch")
+        with torch.cuda.device(dev):
+            word, ws, nbytes = _launch_shape("split", batch_tile, M, N, K, 0, dev)
+            aw = awaiting[:2] if awaiting is not None else (None, None)
+            _lib.check(lib.bi_matmul_push(a2.data_ptr(), bt.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
+                                          a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code, word,
+                                          _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev), *aw, *push))
+        return None
+    out = torch.empty((M, N), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
         word, ws, nbytes = _launch_shape(path, batch_tile, M, N, K, lib.bi_matmul_workspace_bytes(M, N, K, code), dev)
         args = (a2.data_ptr(), bt.data_ptr(), out.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,

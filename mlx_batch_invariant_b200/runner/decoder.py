@@ -43,7 +43,8 @@ class DecoderConfig:
 
 LLAMA3_8B = DecoderConfig()
 
-PUSH_TESTED_WORLDS = (2, 4)  # world sizes at which the peer-memory all-gather has run on hardware
+PUSH_TESTED_WORLDS = (2, 4, 8)  # world sizes at which the peer-memory all-gather has run on hardware
+PUSH_PARTIALS_MAX = 256 << 20   # a matmul pushes its own output only while its split partials stay below this many bytes
 
 
 class TorchGlue:
@@ -100,6 +101,7 @@ class KernelBackend(TorchGlue):
         return out
 
     fused_wait = True       # the kernels can wait for a peer gather themselves (the *_awaiting entry points)
+    fused_push = True       # the matmuls' fold and decode attention's split merge can be the gather (the *_push entry points)
 
     def add_rms_norm(self, x, delta, w, eps, awaiting=None):
         from .. import _lib
@@ -114,12 +116,12 @@ class KernelBackend(TorchGlue):
             _lib.check(_lib.load().bi_add_rms_norm_awaiting(*args, *awaiting, _lib.status_word(x.device).data_ptr()))
         return s, out
 
-    def linear(self, x, w, awaiting=None):       # x[M, K] @ W[N, K]^T
-        return K.batch_invariant_matmul(x, w.T, awaiting=awaiting)
+    def linear(self, x, w, awaiting=None, push=None):       # x[M, K] @ W[N, K]^T
+        return K.batch_invariant_matmul(x, w.T, awaiting=awaiting, push=push)
 
-    def qlinear(self, x, packed, group_size, bits, awaiting=None):
+    def qlinear(self, x, packed, group_size, bits, awaiting=None, push=None):
         p, s, b = packed
-        return K.batch_invariant_quantized_matmul(x, p, s, b, group_size=group_size, bits=bits, awaiting=awaiting)
+        return K.batch_invariant_quantized_matmul(x, p, s, b, group_size=group_size, bits=bits, awaiting=awaiting, push=push)
 
     def rms_norm(self, x, w, eps):
         return K.batch_invariant_rms_norm(x, w, eps)
@@ -127,8 +129,8 @@ class KernelBackend(TorchGlue):
     def prefill_attention(self, q, k, v, scale):
         return K.batch_invariant_prefill_attention(q, k, v, scale=scale, causal=True)
 
-    def decode_attention(self, q, k, v, scale, kv_lens=None):
-        return K.batch_invariant_decode_attention(q, k, v, scale=scale, kv_lens=kv_lens)
+    def decode_attention(self, q, k, v, scale, kv_lens=None, push=None):
+        return K.batch_invariant_decode_attention(q, k, v, scale=scale, kv_lens=kv_lens, push=push)
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -254,6 +256,57 @@ class ShardedDecoder:
         return (getattr(self.ops, "fused_wait", False) and self.dt != torch.float32
                 and os.environ.get("BI_FUSED_WAIT", "1") != "0")
 
+    def _fused_push(self) -> bool:
+        """Whether the kernel that finishes a sharded op's output pushes it to the peers itself (BI_FUSED_PUSH=0
+        keeps the separate gather kernel)."""
+        return (getattr(self.ops, "fused_push", False) and self.dt != torch.float32
+                and os.environ.get("BI_FUSED_PUSH", "1") != "0")
+
+    def _sink(self, rows, cols, defer):
+        """(push arguments, local destination, awaiting) of the next peer gather when a kernel can be that gather
+        for a [rows, cols] slice, else None."""
+        if self.world == 1 or not self._fused_push():
+            return None
+        pg = self._push_gather()
+        if pg is None or not pg.fits(rows, cols * torch.empty(0, dtype=self.dt).element_size()):
+            return None
+        wait = not (defer and self._fused_wait())
+        push, view = pg.sink(rows, cols, self.dt, wait=wait)
+        return push, view, (None if wait else pg.awaiting())
+
+    def _lin_gather(self, x, w, awaiting=None, defer=False):
+        """_gather(_lin(x, w)). With the peer gather and a weight on the tensor-core path the fold kernel of the
+        matmul stores the product into every rank's gathered activation: no local slice, no gather launch."""
+        M, Kdim = x.shape
+        n = (w[0] if self.quant is not None else w).shape[0]
+        groups = (Kdim + 255) // 256
+        tc = Kdim % (64 if self.quant is not None else 8) == 0 and groups * M * n * 4 <= PUSH_PARTIALS_MAX
+        sk = self._sink(M, n, defer) if tc else None
+        if sk is None:
+            out = self._gather(self._lin(x, w, awaiting), defer=defer)
+            return out
+        push, view, aw = sk
+        kw = {"push": push}
+        if awaiting is not None:
+            kw["awaiting"] = awaiting
+        if self.quant is None:
+            self.ops.linear(x, w, **kw)
+        else:
+            self.ops.qlinear(x, w, self.quant[1], self.quant[0], **kw)
+        return (view, aw) if defer else view
+
+    def _attend_gather(self, q, kk, vv, scale, kv_lens=None):
+        """Decode attention of this rank's heads, gathered over the ranks: ([B, hq * world * D], awaiting). With the
+        peer gather the split merge stores straight into every rank's gathered activation."""
+        B, D = q.shape[0], q.shape[3]
+        sk = self._sink(B, self.hq * D, True)
+        if sk is None:
+            a = self.ops.decode_attention(q, kk, vv, scale, kv_lens=kv_lens)
+            return self._gather(a.transpose(1, 2).reshape(B, self.hq * D), defer=True)
+        push, view, aw = sk
+        self.ops.decode_attention(q, kk, vv, scale, kv_lens=kv_lens, push=push)
+        return view, aw
+
     def _gated(self, gu):
         """SwiGLU of this rank's gate/up slice, gathered over the ranks: [M, 2F/R] -> ([M, F], awaiting). With
         the peer gather the gate is computed inside the gather kernel."""
@@ -306,17 +359,17 @@ class ShardedDecoder:
                                      self.kc[li], self.vc[li])
             kk, vv = self.kc[li][:B, :, :end], self.vc[li][:B, :, :end]
             if T == 1:
-                a = self.ops.decode_attention(q, kk, vv, scale)
+                a, aw = self._attend_gather(q, kk, vv, scale)
             else:
                 a = self.ops.prefill_attention(q, kk, vv, scale)
-            a, aw = self._gather(a.transpose(1, 2).reshape(M, self.hq * D), defer=True)
+                a, aw = self._gather(a.transpose(1, 2).reshape(M, self.hq * D), defer=True)
             x, h = self.ops.add_rms_norm(x, self._lin(a, L["o"], aw), L["n2"], cfg.eps)
             act, aw = self._gated(self._lin(h, L["gu"]))
             if li + 1 < len(self.layers):       # the add of this block and the first norm of the next, one launch
-                delta, aw = self._gather(self._lin(act, L["down"], aw), defer=True)
+                delta, aw = self._lin_gather(act, L["down"], aw, defer=True)
                 x, h = self._add_norm(x, delta, self.layers[li + 1]["n1"], aw)
             else:
-                x = x + self._gather(self._lin(act, L["down"], aw))
+                x = x + self._lin_gather(act, L["down"], aw)
             if self.block_hook is not None:
                 self.block_hook(li, x.reshape(B, T, -1))
         last = x.reshape(B, T, -1)[:, -1]
@@ -353,11 +406,10 @@ class GraphedDecoder:
         h = m.ops.rms_norm(x, m.layers[0]["n1"], cfg.eps)
         for li, L in enumerate(m.layers):
             q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
-            a = m.ops.decode_attention(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
-            a, aw = m._gather(a.transpose(1, 2).reshape(B, m.hq * D), defer=True)
+            a, aw = m._attend_gather(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"], aw), L["n2"], cfg.eps)
             act, aw = m._gated(m._lin(h, L["gu"]))
-            delta, aw = m._gather(m._lin(act, L["down"], aw), defer=True)
+            delta, aw = m._lin_gather(act, L["down"], aw, defer=True)
             nxt = m.layers[li + 1]["n1"] if li + 1 < len(m.layers) else m.nf
             x, h = m._add_norm(x, delta, nxt, aw)
         logits = m._gather(m._lin(h, m.head))

@@ -99,6 +99,15 @@ class PushGather:
         *_awaiting entry points)."""
         return (self.bases[self.rank] + NBUF * self.cap, self.counters.data_ptr() + 4, self.rank, self.world)
 
+    def sink(self, rows: int, cols: int, dtype: torch.dtype, wait: bool = True):
+        """The next gather, for a kernel that pushes its own output (``push=`` of the matmuls and of decode
+        attention): returns (push arguments, the local [rows, world * cols] destination). The kernel given the
+        arguments is the gather: it must be launched next on the stream. wait=False: see gather()."""
+        b, dst, flags = self._slot()
+        n = rows * cols * torch.empty(0, dtype=dtype).element_size() * self.world
+        view = self.own[b][:n].view(dtype).view(rows, self.world * cols)
+        return (dst, flags, self.counters.data_ptr(), self.rank, self.world, int(wait)), view
+
     def gather_swiglu(self, gate_up: torch.Tensor, wait: bool = True) -> torch.Tensor:
         """gate_up[rows, 2F] of this rank -> swiglu of every rank's slice, [rows, world * F]: the gate is computed
         while the slice is pushed (one launch; same bits as swiglu followed by gather). wait=False: see gather()."""

@@ -80,3 +80,54 @@ def test_a_flag_that_nothing_raises_runs_the_bounded_wait_out(bi):
         bi.check_device_status()
     assert R.bits_of(bi.batch_invariant_matmul(x, w.T)) == R.bits_of(bi.batch_invariant_matmul(x[:8], w.T, path="fused"))
     bi.check_device_status()
+
+
+def test_ops_that_push_their_own_output(bi):
+    """bi_matmul_push / bi_qmm_push / bi_attn_decode_push as rank 1 of a world of two whose two destinations both
+    live on this GPU: the op's bits land in columns [N, 2N) of BOTH destinations, the other columns stay
+    untouched, the rank's flag goes up at the peer only, and the epoch advances by one per call."""
+    from mlx_batch_invariant_b200.runner.decoder import quantize_rows
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 4096, generator=g).to(dt).cuda()
+    w = (torch.randn(512, 4096, generator=g) / 64).to(dt).cuda()
+    packed = quantize_rows(w, 64, 4)
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    counters = torch.zeros(2, dtype=torch.int32, device="cuda")
+    arr = ctypes.c_void_p * 2
+    epoch = 0
+
+    def pushed(rows, cols, run):
+        nonlocal epoch
+        dst = [torch.zeros(rows, 2 * cols, dtype=dt, device="cuda") for _ in range(2)]
+        push = (arr(dst[0].data_ptr(), dst[1].data_ptr()), arr(flags[0].data_ptr(), flags[1].data_ptr()), counters.data_ptr(), 1, 2, 0)
+        assert run(push) is None
+        epoch += 1
+        assert int(counters[1]) == epoch and int(counters[0]) == 0
+        assert int(flags[0][1]) == epoch and int(flags[1][1]) == 0 and int(flags[0][0]) == 0
+        for d in dst:
+            assert int((d[:, :cols] != 0).sum()) == 0
+        assert R.bits_of(dst[0][:, cols:]) == R.bits_of(dst[1][:, cols:])
+        return dst[0][:, cols:]
+
+    for M in (1, 7, 64):
+        want = bi.batch_invariant_matmul(x[:M], w.T)
+        assert R.bits_of(pushed(M, 512, lambda push: bi.batch_invariant_matmul(x[:M], w.T, push=push))) == R.bits_of(want)
+        want = bi.batch_invariant_quantized_matmul(x[:M], *packed, group_size=64, bits=4)
+        got = pushed(M, 512, lambda push: bi.batch_invariant_quantized_matmul(x[:M], *packed, group_size=64, bits=4, push=push))
+        assert R.bits_of(got) == R.bits_of(want)
+    # the activation itself a gathered buffer that is waited for in the kernel, the output pushed on
+    aw = (flags[1].data_ptr(), counters[1:].data_ptr(), 1, 2)
+    flags[1][0] = epoch                                            # "rank 0" has delivered the gather before this one
+    want = bi.batch_invariant_matmul(x, w.T)
+    assert R.bits_of(pushed(64, 512, lambda push: bi.batch_invariant_matmul(x, w.T, push=push, awaiting=aw))) == R.bits_of(want)
+    flags[1].zero_()
+    for B, L in ((3, 300), (16, 600)):
+        q = torch.randn(B, 4, 1, 128, generator=g).to(dt).cuda()
+        k = torch.randn(B, 1, L, 128, generator=g).to(dt).cuda()
+        v = torch.randn(B, 1, L, 128, generator=g).to(dt).cuda()
+        lens = torch.randint(1, L + 1, (B,), generator=g).to(torch.int32).cuda()
+        want = bi.batch_invariant_decode_attention(q, k, v, scale=0.09, kv_lens=lens).reshape(B, 4 * 128)
+        got = pushed(B, 4 * 128, lambda push: bi.batch_invariant_decode_attention(q, k, v, scale=0.09, kv_lens=lens, push=push))
+        assert R.bits_of(got) == R.bits_of(want)
+    bi.check_device_status()
