@@ -120,6 +120,8 @@ __global__ void __launch_bounds__(128) decode_kernel(const T* __restrict__ q, co
                                                      float* __restrict__ pm, float* __restrict__ pl,
                                                      float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
                                                      KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     constexpr int D = 32 * DL;
     constexpr int NL = NCHUNK * DL;
     const int lane = threadIdx.x & 31;
@@ -267,6 +269,8 @@ __global__ void __launch_bounds__(32 * DEC2_WARPS) decode_stream_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
     float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     using C = Dec2Cfg<T, DL>;
     constexpr int D = 32 * DL;
     constexpr int SEGS = C::ROWB / 16;                 // 16-byte segments per row
@@ -462,6 +466,8 @@ __global__ void __launch_bounds__(32 * MAXW) decode_warp_stream_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
     float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     using C = DecWCfg<T, DL>;
     constexpr int D = 32 * DL;
     constexpr int SEGS = C::ROWB / 16;
@@ -669,6 +675,8 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
     float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     using C = KLCfg;
     constexpr int D = 128;
     extern __shared__ __align__(16) uint8_t dec_smem[];
@@ -833,6 +841,8 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const float* __rest
                                                              const int32_t* __restrict__ kv_lens, T* __restrict__ out,
                                                              int64_t BH, int Hq, int D, int L, int split, int nsplit,
                                                              PushSink sink) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid < BH * D) {
         const int64_t bh = gid / D;
@@ -864,8 +874,8 @@ int launch_decode_combine(const float* pm, const float* pl, const float* pacc, c
                           int Hq, int D, int L, int split, int nsplit, const PushSink* sink, cudaStream_t st) {
     const int64_t n = BH * D;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (sink) decode_combine_kernel<T, true><<<blocks, 256, 0, st>>>(pm, pl, pacc, kv_lens, nullptr, BH, Hq, D, L, split, nsplit, *sink);
-    else decode_combine_kernel<T, false><<<blocks, 256, 0, st>>>(pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, Hq, D, L, split, nsplit, PushSink{});
+    if (sink) launch_overlapped(decode_combine_kernel<T, true>, dim3(blocks), dim3(256), 0, st, pm, pl, pacc, kv_lens, (T*)nullptr, BH, Hq, D, L, split, nsplit, *sink);
+    else launch_overlapped(decode_combine_kernel<T, false>, dim3(blocks), dim3(256), 0, st, pm, pl, pacc, kv_lens, static_cast<T*>(out), BH, Hq, D, L, split, nsplit, PushSink{});
     return check_launch("bi_attn_decode combine");
 }
 
@@ -882,6 +892,8 @@ __global__ void __launch_bounds__(PREFILL_THREADS) prefill_kernel(const T* __res
                                                       const T* __restrict__ v, T* __restrict__ out, int B, int Hq,
                                                       int Hkv, int Tq, int L, KvLayout lay, float scale, int causal,
                                                       int split) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     constexpr int D = 32 * DL;
     constexpr int NL = NCHUNK * DL;
     constexpr int QB = PrefillCfg<DL>::QB;
@@ -1076,7 +1088,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
             attr_set[dev_] = true;                                                                                      \
         }                                                                                                               \
-        kern<<<(unsigned)ctas, 32 * KL_WARPS, KLCfg::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
+        launch_overlapped(kern, dim3((unsigned)ctas), dim3(32 * KL_WARPS), KLCfg::SMEM_BYTES, st, qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
                                                                        (int)Hkv, (int)L, lay, scale, split, nsplit, nck); \
     } while (0)
                 if (nh == 4) BI_KL_LAUNCH(4); else if (nh == 2) BI_KL_LAUNCH(2); else BI_KL_LAUNCH(1);
@@ -1124,7 +1136,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
             attr_set[dev_] = true;                                                                                      \
         }                                                                                                               \
-        kern<<<(unsigned)blocksw, 32 * wpc, smem_w, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv, \
+        launch_overlapped(kern, dim3((unsigned)blocksw), dim3(32 * wpc), smem_w, st, qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, (int)Hkv, \
                                                           (int)L, lay, scale, split, nsplit, nchunk4);                  \
     } while (0)
             if (wpc <= 4) BI_DECW_LAUNCH(4);
@@ -1146,7 +1158,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); \
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e)); \
         }                                                                                                        \
-        kern<<<(unsigned)blocks2, 32 * DEC2_WARPS, C::SMEM_BYTES, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, \
+        launch_overlapped(kern, dim3((unsigned)blocks2), dim3(32 * DEC2_WARPS), C::SMEM_BYTES, st, qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, \
                                                                           (int)Hq, (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk); \
     } while (0)
             if (GU == 4) BI_DECODE2_LAUNCH(4); else if (GU == 2) BI_DECODE2_LAUNCH(2); else BI_DECODE2_LAUNCH(1);
@@ -1160,7 +1172,7 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
     if (lay.table != nullptr)
         return fail(BI_ERR_UNSUPPORTED, "bi_attn_decode_paged: paged caches are read by the 16-bit head_dim-128 kernel only");
 #define BI_DECODE_LAUNCH(GUV)                                                                              \
-    decode_kernel<T, DL, GUV><<<grid, block, 0, st>>>(qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
+    launch_overlapped(decode_kernel<T, DL, GUV>, grid, block, 0, st, qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
                                                       (int)Hkv, (int)L, lay, scale, split, nsplit, nchunk)
     if (GU == 4) {
         if constexpr (DL < 8) BI_DECODE_LAUNCH(4);

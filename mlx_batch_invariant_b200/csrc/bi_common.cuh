@@ -23,6 +23,28 @@ inline int check_launch(const char* what) {
     return BI_OK;
 }
 
+// Defined in abi.cu: whether kernels are launched with programmatic dependent launch (BI_PDL=1 turns it on).
+bool pdl_enabled();
+
+// Launch `kernel` so that it may begin (block scheduling, barrier and tensor-memory set-up) while the kernel before it
+// on the stream is still draining; the kernel itself waits (ptx::grid_dep_wait) before it touches global memory.
+// Every kernel launched through here MUST execute ptx::grid_dep_wait() in every CTA: completion of this kernel then
+// implies completion of everything before it, which is what the kernel after it relies on.
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // errors are picked up by check_launch()
+}
+
 inline bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }
 
 inline size_t dtype_size(int dtype) { return dtype == BI_F32 ? 4 : 2; }

@@ -25,6 +25,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// ---- programmatic dependent launch -----------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while the kernel before it on the
+// stream is still running. grid_dep_wait() blocks until every kernel before this one has completed and its writes
+// are visible (the guarantee of a plain kernel boundary): nothing may read what earlier kernels wrote, and nothing
+// may write global memory at all, before it. grid_dep_launch() lets the kernel AFTER this one start early.
+// Both do nothing in a kernel that was launched the plain way.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -3,6 +3,7 @@
 // round-to-nearest fp32 operations, so these are batch-invariant by construction; they exist to
 // replace a dozen framework launches per layer with two.
 #include "bi_common.cuh"
+#include "bi_ptx.cuh"
 
 namespace bi {
 namespace {
@@ -16,6 +17,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
                                                           T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc,
                                                           int B, int Tn, int Hq, int Hkv, int D, int64_t c_sb, int64_t c_sh,
                                                           int64_t c_sl, int64_t capacity, int32_t* status) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     const int H = Hq + 2 * Hkv;
     const int64_t total = (int64_t)B * Tn * H * D;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -48,6 +51,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const T* __restrict__ 
 // out[m, j] = T( silu(gu[m, j]) * gu[m, F + j] ),  silu(g) = g * sigmoid(g), sigmoid from exp(-|g|)
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t M, int64_t F) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= M * F) return;
     const int64_t m = i / F, j = i - m * F;
@@ -72,7 +77,7 @@ extern "C" int bi_rope_append(const void* qkv, const float* cos_table, const flo
     const int64_t blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_rope_append: too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define BI_ROPE(TT) rope_append_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(qkv), cos_table, sin_table, pos0, \
+#define BI_ROPE(TT) launch_overlapped(rope_append_kernel<TT>, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const TT*>(qkv), cos_table, sin_table, pos0, \
         static_cast<TT*>(q_out), static_cast<TT*>(k_cache), static_cast<TT*>(v_cache), (int)B, (int)T, (int)Hq, (int)Hkv, (int)D, cache_sb, cache_sh, cache_sl, capacity, status)
     if (dtype == BI_F32) BI_ROPE(float); else if (dtype == BI_F16) BI_ROPE(__half); else BI_ROPE(__nv_bfloat16);
 #undef BI_ROPE
@@ -88,8 +93,8 @@ extern "C" int bi_swiglu(const void* gate_up, void* out, int64_t M, int64_t F, i
     const int64_t blocks = (M * F + 255) / 256;
     if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "bi_swiglu: too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == BI_F32) swiglu_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), M, F);
-    else if (dtype == BI_F16) swiglu_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half*>(gate_up), static_cast<__half*>(out), M, F);
-    else swiglu_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), M, F);
+    if (dtype == BI_F32) launch_overlapped(swiglu_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const float*>(gate_up), static_cast<float*>(out), M, F);
+    else if (dtype == BI_F16) launch_overlapped(swiglu_kernel<__half>, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const __half*>(gate_up), static_cast<__half*>(out), M, F);
+    else launch_overlapped(swiglu_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), M, F);
     return check_launch("bi_swiglu");
 }

@@ -15,6 +15,7 @@
 // partials, then combine_kernel folds them). Both perform the same sequence of
 // operations on every element.
 #include "bi_common.cuh"
+#include "bi_ptx.cuh"
 #include "matmul_internal.cuh"
 
 namespace bi {
@@ -44,6 +45,8 @@ __global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restric
                                                               QuantArgs qa, void* __restrict__ outp, int M, int N,
                                                               int K, int64_t a_sm, int64_t a_sk, int64_t b_sk,
                                                               int64_t b_sn) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     constexpr int BM = 16 * TM;
     __shared__ float As[BK][BM];
     __shared__ float Bs[BK][BN];
@@ -139,6 +142,8 @@ __global__ void __launch_bounds__(THREADS) simt_matmul_kernel(const T* __restric
 template <typename T, int VEC, bool PUSH>
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ part, T* __restrict__ out, int G,
                                                       int64_t MN, const T* __restrict__ bias, int64_t N, PushSink sink) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i0 < MN) {
         float total[VEC];
@@ -183,8 +188,8 @@ int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st, 
 #define BI_COMBINE(VEC, THREADS_)                                                                                        \
     do {                                                                                                                 \
         const unsigned blocks_ = (unsigned)(((THREADS_) + 255) / 256);                                                  \
-        if (sink) combine_kernel<T, VEC, true><<<blocks_, 256, 0, st>>>(part, nullptr, G, MN, bias, N, *sink);          \
-        else combine_kernel<T, VEC, false><<<blocks_, 256, 0, st>>>(part, static_cast<T*>(out), G, MN, bias, N, none);  \
+        if (sink) launch_overlapped(combine_kernel<T, VEC, true>, dim3(blocks_), dim3(256), 0, st, part, (T*)nullptr, G, MN, bias, N, *sink); \
+        else launch_overlapped(combine_kernel<T, VEC, false>, dim3(blocks_), dim3(256), 0, st, part, static_cast<T*>(out), G, MN, bias, N, none); \
     } while (0)
     if (vec_ok && MN >= (1 << 20)) {
         BI_COMBINE(4, MN / 4);

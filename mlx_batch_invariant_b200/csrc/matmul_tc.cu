@@ -323,6 +323,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                  const Params p) {
     using C = Cfg<QBITS, TSA>;
     static_assert(!TSA || QBITS != 0, "the tensor-memory weight operand exists for quantized weights only");
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -370,6 +371,9 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
+    // Barriers, tensor memory and the tensor maps were set up while the kernel before this one was still draining;
+    // from here on global memory is touched.
+    ptx::grid_dep_wait();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_total = 2u * (uint32_t)p.acc_stride;
 
@@ -1029,7 +1033,7 @@ int launch_t(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, cuda
     long long grid = p.units < sms ? p.units : sms;
     const long long waves = (p.units + sms - 1) / sms;
     if (waves >= 2 && waves <= 16) grid = (p.units + waves - 1) / waves;
-    kern<<<(unsigned)grid, C::THREADS, p.smem_bytes, st>>>(mw, mx, p);
+    launch_overlapped(kern, dim3((unsigned)grid), dim3(C::THREADS), p.smem_bytes, st, mw, mx, p);
     return check_launch("matmul (tensor-core path)");
 }
 

@@ -29,6 +29,8 @@ namespace {
 __global__ void __launch_bounds__(256) push_gather_kernel(const uint4* __restrict__ local, long long rows, int f16, int rank,
                                                           int R, PeerPtrs dst, PeerPtrs flags, unsigned* counters,
                                                           int32_t* status, int wait) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     const long long total = rows * f16;
     const long long pitch = (long long)R * f16;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -48,6 +50,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) push_gather_swiglu_kernel(const T* __restrict__ gu, long long rows, int F, int rank, int R,
                                                                  PeerPtrs dst, PeerPtrs flags, unsigned* counters,
                                                                  int32_t* status, int wait) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     constexpr int V = 16 / (int)sizeof(T);
     const int f16 = F / V;
     const long long total = rows * f16;
@@ -138,7 +142,7 @@ extern "C" int bi_push_gather(const void* local, void* const* dst, void* const* 
     long long blocks = (total + 256 * 4 - 1) / (256 * 4);   // four 16-byte pieces per thread
     if (blocks > 128) blocks = 128;
     if (blocks < 1) blocks = 1;
-    push_gather_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    launch_overlapped(push_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
         static_cast<const uint4*>(local), rows, (int)f16, rank, world, d, f, counters, status, wait);
     return check_launch("bi_push_gather");
 }
@@ -167,7 +171,7 @@ extern "C" int bi_push_gather_swiglu(const void* gate_up, void* const* dst, void
     if (blocks > 128) blocks = 128;
     if (blocks < 1) blocks = 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define BI_PGS(TT) push_gather_swiglu_kernel<TT><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TT*>(gate_up), rows, (int)F, rank, world, d, f, counters, status, wait)
+#define BI_PGS(TT) launch_overlapped(push_gather_swiglu_kernel<TT>, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const TT*>(gate_up), rows, (int)F, rank, world, d, f, counters, status, wait)
     if (dtype == BI_F32) BI_PGS(float); else if (dtype == BI_F16) BI_PGS(__half); else BI_PGS(__nv_bfloat16);
 #undef BI_PGS
     return check_launch("bi_push_gather_swiglu");

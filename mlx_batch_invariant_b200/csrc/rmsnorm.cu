@@ -18,6 +18,7 @@
 // stores. Rows too long for shared memory, or not 16-byte aligned, take the
 // same arithmetic straight from global memory.
 #include "bi_common.cuh"
+#include "bi_ptx.cuh"
 
 namespace bi {
 namespace {
@@ -56,6 +57,8 @@ struct NormAwait {
 template <typename T, bool STAGED, bool HAS_W, bool HAS_RES>
 __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __restrict__ delta, const T* __restrict__ w,
                                                       T* sum_out, T* __restrict__ out, int D, float eps, NormAwait aw) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     extern __shared__ uint4 stage_raw[];
     __shared__ float red[TG];
     const int t = threadIdx.x;
@@ -168,6 +171,8 @@ __global__ void __launch_bounds__(TG) rms_norm_kernel(const T* x, const T* __res
 template <typename T, bool HAS_W, bool HAS_B>
 __global__ void __launch_bounds__(TG) layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                                                         T* __restrict__ out, int D, float eps) {
+    ptx::grid_dep_launch();   // the next kernel of the stream may start its set-up
+    ptx::grid_dep_wait();     // everything before this kernel has completed and is visible
     __shared__ float red[TG];
     const int t = threadIdx.x;
     const T* xr = x + (size_t)blockIdx.x * (size_t)D;
@@ -253,7 +258,7 @@ int launch(const void* x, const void* delta, const void* w, void* sum_out, void*
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "rms_norm smem attr: %s",               \
                                               cudaGetErrorString(e));                               \
         }                                                                                           \
-        kern<<<grid, block, smem, st>>>(xp, dp, wp, sp, op, (int)D, eps, aw);                           \
+        launch_overlapped(kern, grid, block, smem, st, xp, dp, wp, sp, op, (int)D, eps, aw);                       \
     } while (0)
 #define BI_RMS_LAUNCH(ST, HW) do { if (delta) BI_RMS_LAUNCH2(ST, HW, true); else BI_RMS_LAUNCH2(ST, HW, false); } while (0)
     if (staged) { if (w) BI_RMS_LAUNCH(true, true); else BI_RMS_LAUNCH(true, false); }

@@ -131,3 +131,40 @@ def test_ops_that_push_their_own_output(bi):
         got = pushed(B, 4 * 128, lambda push: bi.batch_invariant_decode_attention(q, k, v, scale=0.09, kv_lens=lens, push=push))
         assert R.bits_of(got) == R.bits_of(want)
     bi.check_device_status()
+
+
+def test_programmatic_dependent_launch_gives_the_same_bits(bi, monkeypatch):
+    """BI_PDL=1 launches the kernels so that each may start while the one before it drains (every kernel waits
+    for its predecessors before it touches global memory). A chain of dependent ops, eagerly and from a replayed
+    CUDA graph, must give the bits of the plain launches."""
+    from mlx_batch_invariant_b200.runner.decoder import KernelBackend
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(16, 1024, generator=g).to(dt).cuda()
+    w1 = (torch.randn(1024, 1024, generator=g) / 32).to(dt).cuda()
+    w2 = (torch.randn(2048, 1024, generator=g) / 32).to(dt).cuda()
+    nw = torch.ones(1024, dtype=dt, device="cuda")
+    q = torch.randn(16, 8, 1, 128, generator=g).to(dt).cuda()
+    k = torch.randn(16, 2, 300, 128, generator=g).to(dt).cuda()
+    v = torch.randn(16, 2, 300, 128, generator=g).to(dt).cuda()
+    ops = KernelBackend()
+
+    def chain():
+        h = bi.batch_invariant_matmul(x, w1.T, path="split")
+        s, h = ops.add_rms_norm(x, h, nw, 1e-5)
+        h = ops.swiglu(bi.batch_invariant_matmul(h, w2.T))
+        a = bi.batch_invariant_decode_attention(q, k, v, scale=0.09).reshape(16, 1024)
+        return bi.batch_invariant_matmul(h + a, w1.T, path="fused"), s
+
+    want = [R.bits_of(t) for t in chain()]
+    monkeypatch.setenv("BI_PDL", "1")
+    assert [R.bits_of(t) for t in chain()] == want
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = chain()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert [R.bits_of(t) for t in outs] == want
+    bi.check_device_status()
