@@ -442,20 +442,21 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 for (; it.valid() && n < LS; it.next(), ++n) issue_w(it);
                 const uint32_t epoch = *p.await.epoch;
                 const uint64_t t0 = ptx::globaltimer_ns();
-                for (int r = 0; r < p.await.world && ok; ++r) {
-                    if (r == p.await.rank) continue;
+                bool arrived = true;                       // lane r watches rank r's flag: the polls overlap
+                if (lane < p.await.world && lane != p.await.rank) {
                     uint32_t seen;
                     do {
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.await.flags + r) : "memory");
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.await.flags + lane) : "memory");
                         if ((int32_t)(seen - epoch) >= 0) break;
                         if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
                             *abort_flag = 1;
-                            if (p.status) atomicCAS(p.status, 0, (int)(0x20000 | (r << 8) | (epoch & 0xff)));
-                            ok = false;
+                            if (p.status) atomicCAS(p.status, 0, (int)(0x20000 | (lane << 8) | (epoch & 0xff)));
+                            arrived = false;
                             break;
                         }
                     } while (true);
                 }
+                if (!__all_sync(0xffffffffu, arrived)) ok = false;
                 asm volatile("fence.proxy.async.global;" ::: "memory");      // peers' stores, seen through the flags, before the TMA reads
                 for (int i = 0; i < n; ++i, first.next()) issue_x(first);   // also after a failed wait: the armed barriers must complete
                 __syncwarp();
