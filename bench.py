@@ -389,7 +389,13 @@ def run_ours(args):
     import mlx_batch_invariant_b200 as bi
     from mlx_batch_invariant_b200 import _lib
     _lib.load()                                            # fail loudly if the CUDA library is missing
-    wl = WORKLOADS[args.workload](torch, bi, dev)
+    wl_cls = WORKLOADS[args.workload]
+    if args.shape:                                         # matmul workloads at another weight shape (config says which)
+        n, k = (int(v) for v in args.shape.split(","))
+        if not hasattr(wl_cls, "N"):
+            raise SystemExit(f"--shape applies to the matmul workloads, not to {args.workload}")
+        wl_cls = type(wl_cls.__name__, (wl_cls,), {"N": n, "K": k})
+    wl = wl_cls(torch, bi, dev)
 
     for i in range(max(args.warmup, 3)):
         wl.step(i)
@@ -777,6 +783,7 @@ def main():
     ap.add_argument("--workload", default="llama3_8b_decode", choices=["llama3_8b_decode", "llama3_8b_decode_q4"] + list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=MODEL_B, choices=[1, 4, 16, 64], help="decoder workloads: sequences per step")
+    ap.add_argument("--shape", default=None, metavar="N,K", help="matmul workloads: weight rows and row length instead of the workload's own")
     ap.add_argument("--no-ops", action="store_true", help="decoder workloads: skip the op-level block of the line")
     args = ap.parse_args()
     model = args.workload.startswith("llama3_8b_decode")
