@@ -242,6 +242,7 @@ struct ChunkIter {
     uint32_t lph, wph, dph;   // phase parities of those rings
     __device__ __forceinline__ ChunkIter(const Params& pp, int ub, int ue) : p(pp), left(ue - ub) {
         ci = 0; l = w = d = 0; lph = wph = dph = 0;
+        nt = mt = g = g1 = nst = c = nchunk = 0;
         if (left <= 0) return;
         int tile;
         if (p.split) { tile = ub / p.G; g = ub - tile * p.G; g1 = g + 1; }
@@ -252,7 +253,7 @@ struct ChunkIter {
     __device__ __forceinline__ void start_group() {
         const int kw = min(p.K - g * GROUP_K, GROUP_K);
         nst = (kw + BLOCK_K - 1) / BLOCK_K;
-        nchunk = p.ks == 4 ? 1 : (nst + p.ks - 1) / p.ks;
+        nchunk = (nst + p.ks - 1) >> (p.ks >> 1);                  // ks is 1, 2 or 4
         c = 0;
     }
     __device__ __forceinline__ bool valid() const { return left > 0; }
@@ -262,22 +263,32 @@ struct ChunkIter {
     __device__ __forceinline__ int k0() const { return g * GROUP_K + c * p.ks * BLOCK_K; }
     __device__ __forceinline__ bool first_in_group() const { return c == 0; }
     __device__ __forceinline__ bool last_in_group() const { return c == nchunk - 1; }
+    // Branch-free on purpose: every role calls this once per chunk, and as a chain of dependent branches it cost
+    // 300-400 cycles a call next to sixteen busy dequantizer warps (a dependent scalar instruction issues about
+    // every ten cycles there). As selects the steps are mostly independent, and a caller can put the call in
+    // front of its arithmetic so that the two interleave. Stepping past the last chunk leaves valid() false and
+    // the other fields meaningless.
     __device__ __forceinline__ void next() {
         ++ci;
-        if (++l == p.load_slots) { l = 0; lph ^= 1u; }
-        if (++w == p.w_ring_slots) { w = 0; wph ^= 1u; }
-        if (++d == MAX_SLOTS) { d = 0; dph ^= 1u; }
-        if (++c < nchunk) return;
-        if (++g < g1) { start_group(); return; }
-        if (--left <= 0) return;
-        if (p.split) {
-            if (g == p.G) { g = 0; if (++mt == p.m_tiles) { mt = 0; ++nt; } }
-            g1 = g + 1;
-        } else {
-            g = 0;
-            if (++mt == p.m_tiles) { mt = 0; ++nt; }
-        }
-        start_group();
+        { const int t = l + 1; const bool wr = t == p.load_slots; l = wr ? 0 : t; lph ^= wr ? 1u : 0u; }
+        { const int t = w + 1; const bool wr = t == p.w_ring_slots; w = wr ? 0 : t; wph ^= wr ? 1u : 0u; }
+        { const int t = d + 1; const bool wr = t == MAX_SLOTS; d = wr ? 0 : t; dph ^= wr ? 1u : 0u; }
+        const int c1 = c + 1, gn = g + 1, mt1 = mt + 1;
+        const bool stay = c1 < nchunk;                              // next chunk of the same K group
+        const bool unit_end = !stay && gn >= g1;                    // else: next group of the same unit
+        const bool tile_adv = unit_end && (!p.split || gn == p.G);  // a split unit is one (tile, group)
+        const bool mwrap = mt1 == p.m_tiles;
+        left -= unit_end ? 1 : 0;
+        mt = tile_adv ? (mwrap ? 0 : mt1) : mt;
+        nt += (tile_adv && mwrap) ? 1 : 0;
+        g = stay ? g : (tile_adv ? 0 : gn);
+        g1 = (unit_end && p.split) ? g + 1 : g1;
+        const int kw = min(p.K - g * GROUP_K, GROUP_K);
+        const int nst_n = (kw + BLOCK_K - 1) >> 6;
+        static_assert(BLOCK_K == 64, "shift above");
+        nchunk = stay ? nchunk : ((nst_n + p.ks - 1) >> (p.ks >> 1));      // ks is 1, 2 or 4
+        nst = stay ? nst : nst_n;
+        c = stay ? c1 : 0;
     }
 };
 
@@ -885,17 +896,19 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const bool two_entries = p.gs == 32;                                 // a K step of 64 spans two quantization groups
         // entries of (row n, K step starting at k): low half = first entry, high half = second (gs 32) or the same
         auto fetch = [&](const ChunkIter& c, uint32_t& sv, uint32_t& bv) {
-            sv = 0u; bv = 0u;
-            if (!c.valid()) return;
+            // Only the loads are issued here. Nothing may touch the loaded value before the chunk it belongs to is
+            // dequantized, DEPTH chunks later: an instruction that uses it now would wait out the whole memory
+            // latency in every iteration. No branches either: where there is nothing to fetch (past the last chunk,
+            // a row beyond N, a K step the chunk does not have) entry 0 is loaded and never used for a stored output.
             const int n = c.n0() + row;
-            if (n >= p.N || jstep >= c.ksteps()) return;
-            const long long e = (long long)n * groups_per_row + ((c.k0() + jstep * BLOCK_K) >> gs_shift);
+            const bool on = c.valid() && n < p.N && jstep < c.ksteps();
+            const long long e = on ? (long long)n * groups_per_row + ((c.k0() + jstep * BLOCK_K) >> gs_shift) : 0ll;
             if (two_entries) {
                 sv = __ldg(reinterpret_cast<const unsigned int*>(scales + e));
                 bv = __ldg(reinterpret_cast<const unsigned int*>(biases + e));
             } else {
-                sv = __ldg(scales + e); sv |= sv << 16;
-                bv = __ldg(biases + e); bv |= bv << 16;
+                sv = __ldg(scales + e);
+                bv = __ldg(biases + e);
             }
         };
         auto to_f = [&](uint32_t h) {
@@ -906,25 +919,35 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         uint32_t qs[DEPTH], qb[DEPTH];
         ChunkIter pf(p, ub, ue);
 #pragma unroll
-        for (int i = 0; i < DEPTH; ++i) { fetch(pf, qs[i], qb[i]); if (pf.valid()) pf.next(); }
+        for (int i = 0; i < DEPTH; ++i) { fetch(pf, qs[i], qb[i]); pf.next(); }
         const uint32_t a_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)p.a_col0;
         bool ok = true;
-        for (ChunkIter it(p, ub, ue); it.valid() && ok; it.next()) {
-            const uint32_t sv = qs[0], bv = qb[0];
+        ChunkIter it(p, ub, ue);
+        while (it.valid() && ok) {
+            uint32_t sv = qs[0], bv = qb[0];
+            if (!two_entries) { sv |= sv << 16; bv |= bv << 16; }             // one entry per K step: both halves use it
 #pragma unroll
             for (int i = 0; i + 1 < DEPTH; ++i) { qs[i] = qs[i + 1]; qb[i] = qb[i + 1]; }
-            fetch(pf, qs[DEPTH - 1], qb[DEPTH - 1]);
-            if (pf.valid()) pf.next();
-            const int l = it.l, w = it.w;
+            const int l = it.l, w = it.w, kst = it.ksteps();
             if (!wait_bounded(bar_lfull(l), it.lph, ctl, ROLE_DEQ, l)) { ok = false; break; }
             if (it.ci >= WS && !wait_done(it.ci - WS, ROLE_DEQ)) { ok = false; break; }
-            if (jstep < it.ksteps()) {
+            // The state of the next iteration and the scale prefetch do not depend on this chunk's data: placed in
+            // front of the arithmetic, in the same basic block, their dependent scalar chains issue in its shadow.
+            auto advance = [&]() {
+                it.next();
+                fetch(pf, qs[DEPTH - 1], qb[DEPTH - 1]);
+                pf.next();
+            };
+            if (jstep < kst) {
+                advance();
                 ptx::tc_fence_after();
                 const float s0 = to_f(sv & 0xffffu), s1 = to_f(sv >> 16), b0 = to_f(bv & 0xffffu), b1 = to_f(bv >> 16);
                 dequant_row64_to_tmem<T, QB>(smem_gen + (raw_chunk(l) - smem_base), row, jstep, ptx::pack2(s0, s0), ptx::pack2(b0, b0),
                                              ptx::pack2(s1, s1), ptx::pack2(b1, b1),
                                              a_lane + (uint32_t)((w * KS + jstep) * TMEM_A_STEP));
                 ptx::tmem_st_wait();
+            } else {
+                advance();
             }
             ptx::tc_fence_before();
             __syncwarp();
