@@ -617,9 +617,13 @@ __global__ void __launch_bounds__(32 * MAXW) decode_warp_stream_kernel(
 //     l = fma(l, corr, p), acc = fma(acc, corr, p * v), the factors read back from shared memory.
 // A warp is one work item (batch, kv head, chunk of NH heads, split) at a time; items are dealt to a
 // persistent grid round-robin, full splits first.
-// Launch-shape constants, from measurements on B200 (bf16, 32/8 heads): seven warps with two K blocks each beat
-// eight or ten warps with one (ten warps cap the kernel at 168 registers: 65 us against 50 us at 64 x 560 keys).
-constexpr int KL_WARPS = 7;    // warps per CTA (one CTA per SM)
+// Launch-shape constants, from measurements on B200 (bf16, 32/8 heads): two K blocks per warp beat one (eight and ten
+// warps with one K block: 53.7 / 65.7 us against 50.1 us with seven warps and two at 64 x 560 keys; ten warps cap the
+// kernel at 168 registers). Eight warps with two K blocks fit once the softmax factors of a block live in that
+// block's own K buffer, which nothing reads after the scores.
+constexpr int KL_WARPS = 8;    // most warps per CTA (one CTA per SM): two per scheduler. With fewer than two work items per
+                               // warp the launch uses seven: each warp is then faster and the tail is what counts
+                               // (64 x 560 keys: 50.1 us with seven, 53.2 with eight; 64 x 4096 keys: 268 against 248 us)
 constexpr int KL_KBUFS = 2;    // K blocks in shared memory per warp: the next block is fetched a whole block ahead
 constexpr int KL_UNROLL = 8;   // keys of the accumulation loop in flight
 constexpr int KL_KEYS = 32;
@@ -630,7 +634,9 @@ struct KLCfg {
     static constexpr int VBUF = KL_KEYS * ROWB;
     static constexpr int QBYTES = 4 * 128 * 4;             // scaled queries of up to four heads, as packed pairs
     static constexpr int CPBYTES = KL_KEYS * 4 * 16;       // (corr, corr, p, p) per key and head
-    static constexpr int WARP_BYTES = KL_KBUFS * KBUF + VBUF + QBYTES + CPBYTES;
+    static constexpr bool CP_IN_KBUF = KL_KBUFS == 2;      // the factors overwrite the block's K rows once the scores exist
+    static_assert(CPBYTES <= KBUF, "the factors of a block must fit its K buffer");
+    static constexpr int WARP_BYTES = KL_KBUFS * KBUF + VBUF + QBYTES + (CP_IN_KBUF ? 0 : CPBYTES);
     static constexpr int SMEM_BYTES = KL_WARPS * WARP_BYTES;
 };
 
@@ -670,8 +676,8 @@ __device__ __forceinline__ void kl_node(const uint8_t* krow, const uint8_t* qs, 
     for (int h = 0; h < NH; ++h) out[h] = ptx::add2_rn(a[h], b[h]);
 }
 
-template <typename T, int NH>
-__global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
+template <typename T, int NH, int NW>
+__global__ void __launch_bounds__(32 * NW, 1) decode_keylane_kernel(
     const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ kv_lens,
     float* __restrict__ pm, float* __restrict__ pl, float* __restrict__ pacc, int B, int Hq, int Hkv, int L,
     KvLayout lay, float scale, int split, int nsplit, int nchunk) {
@@ -685,13 +691,13 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
     uint8_t* kbuf = base;
     uint8_t* vbuf = base + KL_KBUFS * C::KBUF;
     uint8_t* qs = vbuf + C::VBUF;
-    uint8_t* cps = qs + C::QBYTES;
+    uint8_t* const cps_own = qs + C::QBYTES;               // used only when the factors have a buffer of their own
     const uint32_t kbuf_s = (uint32_t)__cvta_generic_to_shared(kbuf), vbuf_s = (uint32_t)__cvta_generic_to_shared(vbuf);
     const int G = Hq / Hkv;
     const long long per_split = (long long)B * Hkv * nchunk;
     const long long items = per_split * nsplit;
 
-    for (long long item = (long long)blockIdx.x * KL_WARPS + wid; item < items; item += (long long)gridDim.x * KL_WARPS) {
+    for (long long item = (long long)blockIdx.x * NW + wid; item < items; item += (long long)gridDim.x * NW) {
         const int sp = (int)(item / per_split);
         long long u = item - (long long)sp * per_split;
         const int chunk = (int)(u % nchunk); u /= nchunk;
@@ -768,7 +774,10 @@ __global__ void __launch_bounds__(32 * KL_WARPS, 1) decode_keylane_kernel(
             const bool valid = lane < cnt;
             // ---- scores of key `lane` for every head
             uint64_t dd[NH];
-            kl_node<T, NH, 1, 0>(kbuf + (KL_KBUFS == 2 ? (blk & 1) * C::KBUF : 0) + lane * C::KPITCH, qs, dd);
+            uint8_t* const kcur = kbuf + (KL_KBUFS == 2 ? (blk & 1) * C::KBUF : 0);
+            kl_node<T, NH, 1, 0>(kcur + lane * C::KPITCH, qs, dd);
+            uint8_t* const cps = C::CP_IN_KBUF ? kcur : cps_own;
+            if (C::CP_IN_KBUF) __syncwarp();                                 // every lane has read its K row: the buffer is free
             // ---- softmax scalars of the block
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
@@ -1075,23 +1084,26 @@ int launch_decode(const void* q, const void* k, const void* v, void* out, const 
                 if (nh > 1 && B * Hkv * ((G + nh - 1) / nh) * nsplit < sms * 4) nh = 1;
                 const int nck = (G + nh - 1) / nh;
                 const int64_t items = B * Hkv * nck * nsplit;
-                const int64_t ctas = std::min<int64_t>(sms, (items + KL_WARPS - 1) / KL_WARPS);
-#define BI_KL_LAUNCH(NHV)                                                                                              \
+                const int nw = items >= 2 * sms * KL_WARPS ? KL_WARPS : KL_WARPS - 1;
+                const int64_t ctas = std::min<int64_t>(sms, (items + nw - 1) / nw);
+#define BI_KL_LAUNCH(NHV, NWV)                                                                                         \
     do {                                                                                                                \
-        auto kern = decode_keylane_kernel<T, NHV>;                                                                      \
+        auto kern = decode_keylane_kernel<T, NHV, (NWV)>;                                                                \
         static bool attr_set[64] = {false};                                                                             \
         int dev_ = 0;                                                                                                   \
         cudaGetDevice(&dev_);                                                                                           \
         if (dev_ < 0 || dev_ >= 64) dev_ = 0;                                                                           \
         if (!attr_set[dev_]) {                                                                                          \
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, KLCfg::SMEM_BYTES); \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (NWV) * KLCfg::WARP_BYTES); \
             if (e != cudaSuccess) return fail(BI_ERR_CUDA, "bi_attn_decode smem attr: %s", cudaGetErrorString(e));      \
             attr_set[dev_] = true;                                                                                      \
         }                                                                                                               \
-        launch_overlapped(kern, dim3((unsigned)ctas), dim3(32 * KL_WARPS), KLCfg::SMEM_BYTES, st, qp, kp, vp, kv_lens, pm, pl, pacc, (int)B, (int)Hq, \
-                                                                       (int)Hkv, (int)L, lay, scale, split, nsplit, nck); \
+        launch_overlapped(kern, dim3((unsigned)ctas), dim3(32 * (NWV)), (size_t)((NWV) * KLCfg::WARP_BYTES), st, qp, kp, vp, kv_lens, pm, pl, pacc, \
+                          (int)B, (int)Hq, (int)Hkv, (int)L, lay, scale, split, nsplit, nck);                           \
     } while (0)
-                if (nh == 4) BI_KL_LAUNCH(4); else if (nh == 2) BI_KL_LAUNCH(2); else BI_KL_LAUNCH(1);
+#define BI_KL_LAUNCH_NH(NWV) do { if (nh == 4) BI_KL_LAUNCH(4, NWV); else if (nh == 2) BI_KL_LAUNCH(2, NWV); else BI_KL_LAUNCH(1, NWV); } while (0)
+                if (nw == KL_WARPS) BI_KL_LAUNCH_NH(KL_WARPS); else BI_KL_LAUNCH_NH(KL_WARPS - 1);
+#undef BI_KL_LAUNCH_NH
 #undef BI_KL_LAUNCH
                 int rck = check_launch("bi_attn_decode (key per lane)");
                 if (rck) return rck;
