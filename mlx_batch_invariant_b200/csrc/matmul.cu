@@ -21,10 +21,14 @@ int64_t ngroups(int64_t K) { return (K + GROUP_K - 1) / GROUP_K; }
 // 64-row tiles 19.7 us against 30.3 us split; M = 128 in 32-row tiles 17.4 against 17.9 us; M = 64 in 16-row
 // tiles 14.8 against 14.5 us). Below that the K groups are spread over CTAs (split) while the fp32 partials
 // stay L2-sized.
-TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K) {
+// Quantized weights at decode (the streaming variant, M <= 8) are bound by the dequantizers' instruction stream, so
+// they want every SM: with fewer weight tiles than SMs they split (the partials of <= 8 rows are tiny) -- 4096 ->
+// 14336 at M = 1: 26.4 us split over 148 CTAs against 27.5 us fused on 112.
+TcShape tc_auto_shape(int64_t M, int64_t N, int64_t K, bool quant = false) {
     TcShape sh{false, 128, nullptr, TcShape::STAGE_AUTO, Await{nullptr, nullptr, 0, 0}, nullptr};
     const int64_t G = ngroups(K);
     const int64_t nt = (N + 127) / 128;
+    if (quant && M <= 8 && G > 1 && nt < sm_count()) { sh.split = true; return sh; }
     const int64_t fill = (int64_t)sm_count() * 3 / 4;
     int bm_fill = 0;                               // tallest batch tile that still fills the GPU
     for (int bm = 128; bm >= 16; bm >>= 1)
@@ -61,8 +65,8 @@ int parse_path(const char* op, int path, PathArg* pa) {
 // Resolve the launch shape of a tensor-core call and lay out the workspace: [counter block, if the caller says
 // it keeps one][fp32 partials].
 int tc_shape(const char* op, const PathArg& pa, void* ws, size_t ws_bytes, int64_t M, int64_t N, int64_t K,
-             TcShape* sh, float** part) {
-    *sh = tc_auto_shape(M, N, K);
+             TcShape* sh, float** part, bool quant = false) {
+    *sh = tc_auto_shape(M, N, K, quant);
     if (pa.kind == BI_MATMUL_SPLIT || pa.kind == BI_MATMUL_SPLIT_FOLD) { sh->split = true; sh->bm = 128; }
     if (pa.kind == BI_MATMUL_FUSED && sh->split) {
         sh->split = false;
@@ -119,7 +123,11 @@ extern "C" size_t bi_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int
 }
 
 extern "C" size_t bi_qmm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
-    return bi_matmul_workspace_bytes(M, N, K, dtype);
+    using namespace bi;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (dtype == BI_F32 || ngroups(K) <= 1) return bi_matmul_workspace_bytes(M, N, K, dtype);
+    if (!tc_auto_shape(M, N, K, true).split) return 0;
+    return COUNTER_BYTES + (size_t)ngroups(K) * (size_t)M * (size_t)N * sizeof(float);
 }
 
 namespace bi {
@@ -238,7 +246,7 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
         if (!aligned(x, 16) || (x_ld * (int64_t)es) % 16 != 0)
             return fail(BI_ERR_MISALIGNED, "bi_qmm: activation must have 16-byte aligned rows for this weight");
         TcShape sh;
-        rc = tc_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &sh, &part);
+        rc = tc_shape("bi_qmm", pa, workspace, workspace_bytes, M, N, K, &sh, &part, true);
         if (rc) return rc;
         sh.await = aw;
         rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, part, M, N, K, dtype, sh, status, st);

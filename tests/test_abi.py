@@ -90,5 +90,7 @@ def test_workspace_sizes_follow_the_auto_launch_shape():
     assert f(16, 4096, 4096, _lib.BI_F32) == CB + 16 * 16 * 4096 * 4        # fp32: the CUDA-core rule (split up to 32 rows)
     assert f(64, 4096, 4096, _lib.BI_F32) == 0
     assert L.bi_qmm_workspace_bytes(16, 14336, 4096, _lib.BI_BF16) == 0     # 112 tiles: fused
+    assert L.bi_qmm_workspace_bytes(1, 14336, 4096, _lib.BI_BF16) == CB + 16 * 1 * 14336 * 4   # decode: fewer tiles than SMs -> split
+    assert L.bi_qmm_workspace_bytes(1, 28672, 4096, _lib.BI_BF16) == 0      # 224 tiles: fused
     assert L.bi_qmm_workspace_bytes(16, 4096, 4096, _lib.BI_BF16) == CB + 16 * 16 * 4096 * 4
     assert f(0, 4096, 4096, _lib.BI_BF16) == 0
