@@ -1,8 +1,10 @@
 """The pieces of the fused peer gather that one GPU can check: the gather kernel that computes the SwiGLU gate
-on the way (world of one: the destination is local memory), and the *_awaiting entry points -- with the peers'
+on the way (world of one: the destination is local memory), the *_awaiting entry points -- with the peers'
 flags already raised they give the bits of the plain entry points; with a flag that nothing raises the bounded
-wait runs out, the status word says so, and the context stays usable. (The exchange between GPUs itself is
-covered by tests/test_gpu_multi.py.)"""
+wait runs out, the status word says so, and the context stays usable --, the *_push entry points (matmul,
+quantized matmul, decode attention) as one rank of a world of two whose destinations both live on this GPU, and
+the kernels launched with programmatic dependent launch. (The exchange between GPUs itself is covered by
+tests/test_gpu_multi.py.)"""
 
 import ctypes
 import time
