@@ -884,7 +884,7 @@ tc_matmul_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // packed columns with one tcgen05.st. Scales and biases are read straight from global memory,
         // DEPTH chunks ahead of their use (a register queue), through the L1.
         constexpr int QB = QBITS ? QBITS : 4;
-        constexpr int DEPTH = 4;
+        constexpr int DEPTH = 2;   // chunks between a scale load and its use (each load touches 32 lines: a deeper queue only lengthens the burst before the first chunk)
         const int dw = warp - WARP_DEQ0;
         const int quad = warp & 3;
         const int jstep = dw >> 2;                                           // 0..3
