@@ -657,8 +657,13 @@ def run_model(args, quant):
         achieved = bytes_step / per / 1e9
         gather = "none (single GPU)"
         if world > 1:
-            gather = ("peer-memory push all-gather (bi_push_gather), 97 per step" if model._pg is not None
-                      else "NCCL all_gather_into_tensor, 97 per step")
+            if model._pg is None:
+                gather = "NCCL all_gather_into_tensor, 97 per step"
+            elif model._fused_push():
+                gather = ("peer-memory push over NVLink, 97 per step: 96 fused into the producing kernels (attention merge, "
+                          "SwiGLU, down-projection fold) with the wait in the consumer, 1 stand-alone (logits)")
+            else:
+                gather = "peer-memory push all-gather (bi_push_gather), 97 per step"
         from oracle import reference as R
         cores = os.cpu_count() or 1
         R.set_threads(cores)                                # torchrun pins OMP_NUM_THREADS to 1; the baseline uses every core

@@ -20,6 +20,7 @@ from __future__ import annotations
 import hashlib
 import math
 import os
+import sys
 from dataclasses import dataclass
 
 import torch
@@ -327,10 +328,20 @@ class ShardedDecoder:
             mode = os.environ.get("BI_GATHER", "")
             if mode == "nccl" or (mode != "push" and self.world not in PUSH_TESTED_WORLDS):
                 return None
-            from .peer import PushGather
+            if getattr(self, "_pg_unavailable", False):
+                return None
+            from .peer import PeerUnavailable, PushGather
             es = torch.empty(0, dtype=self.dt).element_size()
             widest = max(self.cfg.vocab, self.cfg.ffn, self.cfg.d_model, self.hq * self.world * self.cfg.head_dim)
-            self._pg = PushGather(self.group, self.rank, self.world, self.dev, self.max_batch * widest * es)
+            try:
+                self._pg = PushGather(self.group, self.rank, self.world, self.dev, self.max_batch * widest * es)
+            except PeerUnavailable as e:      # raised on all ranks together: all of them take the library collective
+                if mode == "push":
+                    raise
+                self._pg_unavailable = True
+                if self.rank == 0:
+                    print(f"peer-memory gather unavailable, using NCCL all-gather: {e}", file=sys.stderr)
+                return None
         return self._pg
 
     def check_capacity(self, batch: int, end: int) -> None:

@@ -39,6 +39,10 @@ def pick_cycle(n: int, mod: int, calls: int) -> tuple[int, int]:
     raise RuntimeError(f"no buffer rotation for a cycle of {n} gathers")
 
 
+class PeerUnavailable(RuntimeError):
+    """Some pair of ranks cannot map each other's memory; raised on every rank of the group together."""
+
+
 class _Raw:
     """A device pointer as something torch.as_tensor can wrap (no copy, no ownership)."""
 
@@ -60,14 +64,26 @@ class PushGather:
             _lib.check(self.lib.bi_peer_export(base, handle))
             handles = [None] * world
             dist.all_gather_object(handles, handle.raw, group=group)
-            self.bases = []
+            self.bases, failure = [], None
             for r in range(world):
                 if r == rank:
                     self.bases.append(base.value)
-                else:
-                    p = ctypes.c_void_p()
+                    continue
+                p = ctypes.c_void_p()
+                try:
                     _lib.check(self.lib.bi_peer_open(handles[r], ctypes.byref(p)))
-                    self.bases.append(p.value)
+                except _lib.KernelError as e:           # no peer mapping to rank r from here (no NVLink / IPC between the two)
+                    failure = failure or f"rank {rank} cannot map rank {r}'s buffer: {e}"
+                self.bases.append(p.value)
+            # Every rank must come to the same verdict, or the ones that succeeded would wait for the others forever.
+            verdicts = [None] * world
+            dist.all_gather_object(verdicts, failure, group=group)
+            if any(verdicts):
+                for r, b in enumerate(self.bases):
+                    if r != rank and b:
+                        self.lib.bi_peer_close(ctypes.c_void_p(b))
+                self.lib.bi_peer_free(base)
+                raise PeerUnavailable("; ".join(v for v in verdicts if v))
             self.own = [torch.as_tensor(_Raw(base.value + b * self.cap, self.cap), device=device) for b in range(NBUF)]
             self.counters = torch.zeros(2, dtype=torch.int32, device=device)
         self.calls = 0
