@@ -305,6 +305,23 @@ int bi_attn_decode_push(const void* q, const void* k, const void* v, const int32
                         void* stream, void* const* dst, void* const* peer_flags, uint32_t* counters, int rank,
                         int world, int wait, int32_t* status);
 
+/* The qkv projection of a decoder with bi_rope_append folded into it: bi_matmul / bi_qmm (tensor-core weights only;
+ * always the split launch shape: the workspace must hold ceil(K/256) * M * N * 4 bytes, + BI_MATMUL_COUNTER_BYTES
+ * with BI_MATMUL_WS_ZEROED) whose fold kernel rounds the product [B*T, (Hq + 2*Hkv) * D] to the dtype and then does
+ * what bi_rope_append does with it -- rotated q into q_out, rotated k and plain v into the caches at position
+ * pos0[0] + t, positions outside `capacity` skipped with 0x30000 | position in *status. The product itself is never
+ * stored. Same bits as bi_matmul / bi_qmm followed by bi_rope_append. No counterpart in the reference. */
+int bi_matmul_rope(const void* a, const void* b, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                   int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, int path,
+                   int32_t* status, void* stream, const float* cos_table, const float* sin_table,
+                   const int64_t* pos0, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq,
+                   int64_t Hkv, int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity);
+int bi_qmm_rope(const void* x, const uint32_t* w, const void* scales, const void* biases, void* workspace,
+                size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm, int group_size, int bits,
+                int dtype, int path, int32_t* status, void* stream, const float* cos_table, const float* sin_table,
+                const int64_t* pos0, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq,
+                int64_t Hkv, int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

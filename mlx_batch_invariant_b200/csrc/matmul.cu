@@ -142,11 +142,11 @@ int check_await(const char* op, const Await& aw) {
 int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t workspace_bytes, int64_t M,
                 int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype,
                 int path, int32_t* status, void* stream, const Await& aw, const void* bias = nullptr,
-                const PushSink* sink = nullptr) {
+                const PushSink* sink = nullptr, const RopeSink* rope = nullptr) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dtype %d", dtype);
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_matmul: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (M == 0 || N == 0) return BI_OK;
-    if (!a || !b || (!out && !sink)) return fail(BI_ERR_BAD_ARG, "bi_matmul: null pointer");
+    if (!a || !b || (!out && !sink && !rope)) return fail(BI_ERR_BAD_ARG, "bi_matmul: null pointer");
     if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "bi_matmul: dimension too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t es = dtype_size(dtype);
@@ -158,8 +158,8 @@ int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t
     PathArg pa;
     int rc = parse_path("bi_matmul", path, &pa);
     if (rc) return rc;
-    if (sink) {      // the fold kernel is the one that pushes: always the split shape, folded by the second launch
-        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_push: only weights on the tensor-core path can push their output");
+    if (sink || rope) {      // the fold kernel is the one that pushes / rotates: always the split shape, folded by the second launch
+        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_push / bi_matmul_rope: only weights on the tensor-core path");
         pa.kind = BI_MATMUL_SPLIT;
     }
     float* part = nullptr;
@@ -175,6 +175,7 @@ int matmul_impl(const void* a, const void* b, void* out, void* workspace, size_t
         const int64_t w_ld = N == 1 ? K : b_sn;
         rc = launch_tc_matmul(a, x_ld, b, w_ld, nullptr, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
+        if (rope) return launch_combine_rope(part, (int)ngroups(K), M * N, dtype, st, *rope);
         return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, bias, N, sink);
     }
     if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_matmul_awaiting: only weights on the tensor-core path can wait for a gather");
@@ -217,7 +218,7 @@ namespace {
 int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* biases, void* out,
              void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm,
              int group_size, int bits, int dtype, int path, int32_t* status, void* stream, const Await& aw,
-             const PushSink* sink = nullptr) {
+             const PushSink* sink = nullptr, const RopeSink* rope = nullptr) {
     if (!dtype_ok(dtype)) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: dtype %d", dtype);
     if (bits != 4 && bits != 8) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: bits=%d (supported: 4, 8)", bits);
     if (group_size != 32 && group_size != 64 && group_size != 128)
@@ -225,7 +226,7 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
     if (M < 0 || N < 0 || K <= 0) return fail(BI_ERR_BAD_ARG, "bi_qmm: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
     if (K % group_size != 0) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: K=%lld is not a multiple of group_size=%d", (long long)K, group_size);
     if (M == 0 || N == 0) return BI_OK;
-    if (!x || !w || !scales || !biases || (!out && !sink)) return fail(BI_ERR_BAD_ARG, "bi_qmm: null pointer");
+    if (!x || !w || !scales || !biases || (!out && !sink && !rope)) return fail(BI_ERR_BAD_ARG, "bi_qmm: null pointer");
     if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return fail(BI_ERR_UNSUPPORTED, "bi_qmm: dimension too large");
     if (M > 1 && x_sm < K) return fail(BI_ERR_BAD_ARG, "bi_qmm: row stride %lld < K", (long long)x_sm);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -236,8 +237,8 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
     PathArg pa;
     int rc = parse_path("bi_qmm", path, &pa);
     if (rc) return rc;
-    if (sink) {
-        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_push: only weights on the tensor-core path can push their output");
+    if (sink || rope) {
+        if (!weight_tc) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_push / bi_qmm_rope: only weights on the tensor-core path");
         pa.kind = BI_MATMUL_SPLIT;
     }
     float* part = nullptr;
@@ -251,6 +252,7 @@ int qmm_impl(const void* x, const uint32_t* w, const void* scales, const void* b
         sh.await = aw;
         rc = launch_tc_matmul(x, x_ld, nullptr, 0, &q, out, part, M, N, K, dtype, sh, status, st);
         if (rc || !sh.split || sh.counters) return rc;
+        if (rope) return launch_combine_rope(part, (int)ngroups(K), M * N, dtype, st, *rope);
         return launch_combine(part, out, (int)ngroups(K), M * N, dtype, st, nullptr, N, sink);
     }
     if (aw.flags) return fail(BI_ERR_UNSUPPORTED, "bi_qmm_awaiting: only weights on the tensor-core path can wait for a gather");
@@ -310,4 +312,48 @@ extern "C" int bi_qmm_push(const void* x, const uint32_t* w, const void* scales,
     if (rc) return rc;
     return qmm_impl(x, w, scales, biases, nullptr, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
                     stream, aw, &sink);
+}
+
+// ---- qkv projection whose fold applies the rotary embedding and appends to the KV cache ----
+namespace bi {
+namespace {
+int make_rope(const char* op, int64_t M, int64_t N, const float* cos_table, const float* sin_table, const int64_t* pos0, void* q_out,
+              void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t c_sb, int64_t c_sh,
+              int64_t c_sl, int64_t capacity, int32_t* status, RopeSink* r) {
+    if (B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || D % 2 || capacity <= 0) return fail(BI_ERR_BAD_ARG, "%s: bad sizes", op);
+    if (M != B * T || N != (Hq + 2 * Hkv) * D)
+        return fail(BI_ERR_BAD_ARG, "%s: the product must be [B*T, (Hq + 2*Hkv) * D] (M=%lld N=%lld)", op, (long long)M, (long long)N);
+    if (!cos_table || !sin_table || !pos0 || !q_out || !k_cache || !v_cache) return fail(BI_ERR_BAD_ARG, "%s: null pointer", op);
+    *r = RopeSink{cos_table, sin_table, pos0, q_out, k_cache, v_cache, (int)B, (int)T, (int)Hq, (int)Hkv, (int)D, c_sb, c_sh, c_sl, capacity, status};
+    return BI_OK;
+}
+}  // namespace
+}  // namespace bi
+
+extern "C" int bi_matmul_rope(const void* a, const void* b, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                              int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, int path,
+                              int32_t* status, void* stream, const float* cos_table, const float* sin_table,
+                              const int64_t* pos0, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq,
+                              int64_t Hkv, int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity) {
+    using namespace bi;
+    RopeSink rope;
+    int rc = make_rope("bi_matmul_rope", M, N, cos_table, sin_table, pos0, q_out, k_cache, v_cache, B, T, Hq, Hkv, D, cache_sb,
+                       cache_sh, cache_sl, capacity, status, &rope);
+    if (rc) return rc;
+    return matmul_impl(a, b, nullptr, workspace, workspace_bytes, M, N, K, a_sm, a_sk, b_sk, b_sn, dtype, path, status, stream,
+                       Await{nullptr, nullptr, 0, 0}, nullptr, nullptr, &rope);
+}
+
+extern "C" int bi_qmm_rope(const void* x, const uint32_t* w, const void* scales, const void* biases, void* workspace,
+                           size_t workspace_bytes, int64_t M, int64_t N, int64_t K, int64_t x_sm, int group_size, int bits,
+                           int dtype, int path, int32_t* status, void* stream, const float* cos_table, const float* sin_table,
+                           const int64_t* pos0, void* q_out, void* k_cache, void* v_cache, int64_t B, int64_t T, int64_t Hq,
+                           int64_t Hkv, int64_t D, int64_t cache_sb, int64_t cache_sh, int64_t cache_sl, int64_t capacity) {
+    using namespace bi;
+    RopeSink rope;
+    int rc = make_rope("bi_qmm_rope", M, N, cos_table, sin_table, pos0, q_out, k_cache, v_cache, B, T, Hq, Hkv, D, cache_sb,
+                       cache_sh, cache_sl, capacity, status, &rope);
+    if (rc) return rc;
+    return qmm_impl(x, w, scales, biases, nullptr, workspace, workspace_bytes, M, N, K, x_sm, group_size, bits, dtype, path, status,
+                    stream, Await{nullptr, nullptr, 0, 0}, nullptr, &rope);
 }

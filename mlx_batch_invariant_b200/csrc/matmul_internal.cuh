@@ -13,6 +13,22 @@ namespace bi {
 int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias = nullptr,
                    int64_t N = 1, const PushSink* sink = nullptr);
 
+// The qkv projection of a decoder: where the fold of its split partials sends the result instead of `out` -- rotated q
+// into q_out[B, Hq, T, D], rotated k and plain v into the caches at position pos0[0] + t (the arguments of
+// bi_rope_append, whose arithmetic and capacity guard the fold kernel repeats element for element).
+struct RopeSink {
+    const float* cos_table;
+    const float* sin_table;
+    const int64_t* pos0;
+    void* q_out;
+    void* k_cache;
+    void* v_cache;
+    int B, T, Hq, Hkv, D;
+    int64_t c_sb, c_sh, c_sl, capacity;
+    int32_t* status;
+};
+int launch_combine_rope(const float* part, int G, int64_t MN, int dtype, cudaStream_t st, const RopeSink& rope);
+
 // CUDA-core path (fp32 inputs, or weights TMA cannot address).
 int launch_simt_matmul(const void* a, const void* b, void* out, float* part, int64_t M, int64_t N, int64_t K,
                        int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int dtype, bool split,

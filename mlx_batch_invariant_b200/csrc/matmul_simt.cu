@@ -202,6 +202,48 @@ int combine_t(const float* part, void* out, int G, int64_t MN, cudaStream_t st, 
     return check_launch("matmul combine");
 }
 
+// The fold of the split path for a decoder's qkv projection, with bi_rope_append's work done on the folded values
+// before they ever reach memory. One thread per element, as in combine_kernel (enough loads in flight to cover the
+// L2 latency): it folds its column, rounds to T (the bits combine_kernel would have stored), leaves the value in shared
+// memory for the thread that holds the other half of the rotation pair (a block of 256 consecutive elements covers
+// whole heads: 256 % D == 0), and then repeats rope_append_kernel's arithmetic: q and k heads rotated, v heads
+// copied, positions outside the cache skipped with a status code.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_rope_kernel(const float* __restrict__ part, int G, int64_t MN, RopeSink r) {
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
+    __shared__ T rounded[256];
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = i < MN;
+    float total = 0.0f;
+    if (live)
+        for (int g = 0; g < G; ++g) total = add_rn(total, part[(int64_t)g * MN + i]);
+    const T x = Cvt<T>::down(total);
+    rounded[threadIdx.x] = x;
+    __syncthreads();
+    if (!live) return;
+    const int H = r.Hq + 2 * r.Hkv, half = r.D / 2;
+    const int d = (int)(i % r.D);
+    const int h = (int)((i / r.D) % H);
+    const int64_t bt = i / ((int64_t)r.D * H);
+    const int t = (int)(bt % r.T);
+    const int b = (int)(bt / r.T);
+    const int64_t pos = r.pos0[0] + t;
+    if (pos < 0 || pos >= r.capacity) {
+        if (r.status) atomicCAS(r.status, 0, (int)(0x30000 | (int)(pos & 0xffff)));
+        return;
+    }
+    if (h >= r.Hq + r.Hkv) {                               // v: stored as is
+        static_cast<T*>(r.v_cache)[(int64_t)b * r.c_sb + (int64_t)(h - r.Hq - r.Hkv) * r.c_sh + pos * r.c_sl + d] = x;
+        return;
+    }
+    const float other = Cvt<T>::up(rounded[d < half ? threadIdx.x + half : threadIdx.x - half]);
+    const float rot = d < half ? -other : other;
+    const T o = Cvt<T>::down(add_rn(mul_rn(Cvt<T>::up(x), r.cos_table[pos * r.D + d]), mul_rn(rot, r.sin_table[pos * r.D + d])));
+    if (h < r.Hq) static_cast<T*>(r.q_out)[(((int64_t)b * r.Hq + h) * r.T + t) * r.D + d] = o;
+    else          static_cast<T*>(r.k_cache)[(int64_t)b * r.c_sb + (int64_t)(h - r.Hq) * r.c_sh + pos * r.c_sl + d] = o;
+}
+
 template <typename T, bool QUANT>
 int simt_t(const void* a, const void* b, const QuantArgs& qa, void* out, float* part, int64_t M, int64_t N,
            int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, bool split, cudaStream_t st) {
@@ -223,6 +265,18 @@ int simt_t(const void* a, const void* b, const QuantArgs& qa, void* out, float* 
 }
 
 }  // namespace
+
+int launch_combine_rope(const float* part, int G, int64_t MN, int dtype, cudaStream_t st, const RopeSink& rope) {
+    if (rope.D > 256 || 256 % rope.D != 0) return fail(BI_ERR_UNSUPPORTED, "matmul + rope: head_dim %d (must divide 256)", rope.D);
+    const int64_t blocks = (MN + 255) / 256;
+    if (blocks > 0x7fffffffLL) return fail(BI_ERR_UNSUPPORTED, "matmul + rope: too large");
+    switch (dtype) {
+        case BI_F32: launch_overlapped(combine_rope_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, st, part, G, MN, rope); break;
+        case BI_F16: launch_overlapped(combine_rope_kernel<__half>, dim3((unsigned)blocks), dim3(256), 0, st, part, G, MN, rope); break;
+        default:     launch_overlapped(combine_rope_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, st, part, G, MN, rope); break;
+    }
+    return check_launch("matmul fold + rope");
+}
 
 int launch_combine(const float* part, void* out, int G, int64_t MN, int dtype, cudaStream_t st, const void* bias, int64_t N,
                    const PushSink* sink) {

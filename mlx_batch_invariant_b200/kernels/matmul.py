@@ -39,7 +39,8 @@ def _weight_is_tensor_core(b: torch.Tensor, K: int) -> bool:
             and (b.shape[1] == 1 or ((b.stride(1) * es) % 16 == 0 and b.stride(1) >= K)))
 
 
-def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None, bias=None, push=None):
+def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None = None, awaiting=None, bias=None, push=None,
+                           rope=None):
     """``a @ b`` with a batch-invariant reduction order.
 
     ``a`` may have extra leading dims (flattened into M); ``b`` must be 2-D (a transposed
@@ -52,6 +53,9 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
     ``push`` (destination table, flag table, counters pointer, rank, world, wait -- ``PushGather.sink()``): the
     product is this rank's column slice of a gathered activation; the fold kernel stores it into every rank's
     destination and shakes hands (``bi_matmul_push``); nothing is returned.
+    ``rope`` (the arguments of ``bi_rope_append`` after ``qkv``, up to ``capacity``): the product is a decoder's qkv
+    projection; the fold kernel rotates q and k and appends k and v to the cache itself (``bi_matmul_rope``);
+    nothing is returned.
     """
     at, foreign = adopt(a)
     bt, _ = adopt(b)
@@ -78,6 +82,15 @@ def batch_invariant_matmul(a, b, *, path: str = "auto", batch_tile: int | None =
     if M > 0 and _weight_is_tensor_core(bt, K):
         a2 = rows_16b(a2)
     lib = _lib.load()
+    if rope is not None:
+        if bias is not None or push is not None or awaiting is not None or M == 0:
+            raise ValueError("rope cannot be combined with bias, push, awaiting or an empty batch")
+        with torch.cuda.device(dev):
+            word, ws, nbytes = _launch_shape("split", batch_tile, M, N, K, 0, dev)
+            _lib.check(lib.bi_matmul_rope(a2.data_ptr(), bt.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
+                                          a2.stride(0) if M > 1 else K, a2.stride(1), bt.stride(0), bt.stride(1), code, word,
+                                          _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev), *rope))
+        return None
     if push is not None:
         if bias is not None or M == 0:
             raise ValueError("push cannot be combined with bias or an empty batch")

@@ -42,10 +42,12 @@ _STAGES = {None: 0, "smem": _lib.QMM_STAGE_SMEM, "tmem": _lib.QMM_STAGE_TMEM}
 
 
 def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, bits: int, path: str = "auto",
-                                     batch_tile: int | None = None, stage: str | None = None, awaiting=None, push=None):
+                                     batch_tile: int | None = None, stage: str | None = None, awaiting=None, push=None,
+                                     rope=None):
     """``x @ dequant(w).T``. ``path`` / ``batch_tile`` force a launch shape as for the dense matmul; ``stage``
     ("smem", "tmem") forces how the dequantized weight reaches the tensor core. All give the same bits.
-    ``awaiting`` / ``push``: as for ``batch_invariant_matmul`` (``bi_qmm_awaiting`` / ``bi_qmm_push``)."""
+    ``awaiting`` / ``push`` / ``rope``: as for ``batch_invariant_matmul`` (``bi_qmm_awaiting`` / ``bi_qmm_push`` /
+    ``bi_qmm_rope``)."""
     xt, foreign = adopt(x)
     wt, st, bt = adopt(w)[0], adopt(scales)[0], adopt(biases)[0]
     dev = require_cuda(xt, wt, st, bt)
@@ -66,6 +68,15 @@ def batch_invariant_quantized_matmul(x, w, scales, biases, *, group_size: int, b
     bt = bt.to(dt).contiguous()
     wt = wt.contiguous()
     lib = _lib.load()
+    if rope is not None:
+        if push is not None or awaiting is not None or M == 0:
+            raise ValueError("rope cannot be combined with push, awaiting or an empty batch")
+        with torch.cuda.device(dev):
+            word, ws, nbytes = _launch_shape("split", batch_tile, M, N, K, 0, dev)
+            _lib.check(lib.bi_qmm_rope(x2.data_ptr(), wt.data_ptr(), st.data_ptr(), bt.data_ptr(), _lib.ptr(ws), nbytes, M, N, K,
+                                       x2.stride(0) if M > 1 else K, group_size, bits, code, word | _STAGES[stage],
+                                       _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev), *rope))
+        return None
     if push is not None:
         if M == 0:
             raise ValueError("push cannot be combined with an empty batch")

@@ -101,6 +101,21 @@ class KernelBackend(TorchGlue):
                                          _lib.stream_ptr(gu.device)))
         return out
 
+    fused_rope = True       # the fold of the qkv projection can rotate and append itself (bi_matmul_rope / bi_qmm_rope)
+
+    def linear_rope(self, x, w, quant, cos, sin, pos0, B, T, hq, hkv, D, kc, vc):
+        """rope_append(linear(x, w)) in the matmul's own two launches: returns the rotated q [B, hq, T, D]."""
+        from .. import _lib  # noqa: F401  (the library must be loadable)
+        q = torch.empty(B, hq, T, D, dtype=x.dtype, device=x.device)
+        rope = (cos.data_ptr(), sin.data_ptr(), pos0.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T, hq, hkv, D,
+                kc.stride(0), kc.stride(1), kc.stride(2), min(kc.shape[2], cos.shape[0]))
+        if quant is None:
+            K.batch_invariant_matmul(x, w.T, rope=rope)
+        else:
+            p, s, b = w
+            K.batch_invariant_quantized_matmul(x, p, s, b, group_size=quant[1], bits=quant[0], rope=rope)
+        return q
+
     fused_wait = True       # the kernels can wait for a peer gather themselves (the *_awaiting entry points)
     fused_push = True       # the matmuls' fold and decode attention's split merge can be the gather (the *_push entry points)
 
@@ -257,6 +272,22 @@ class ShardedDecoder:
         return (getattr(self.ops, "fused_wait", False) and self.dt != torch.float32
                 and os.environ.get("BI_FUSED_WAIT", "1") != "0")
 
+    def _qkv(self, h, w, pos0, B, T, kc, vc):
+        """The qkv projection, rotary embedding and cache append of a block: rotated q [B, hq, T, D]. With a weight
+        on the tensor-core path and decode-sized partials the fold of the projection does all of it
+        (BI_FUSED_ROPE=0 keeps the separate kernel)."""
+        D = self.cfg.head_dim
+        M, Kdim = h.shape
+        n = (w[0] if self.quant is not None else w).shape[0]
+        fused = (getattr(self.ops, "fused_rope", False) and self.dt != torch.float32
+                 and os.environ.get("BI_FUSED_ROPE", "1") != "0"
+                 and Kdim % (64 if self.quant is not None else 8) == 0
+                 and ((Kdim + 255) // 256) * M * n * 4 <= PUSH_PARTIALS_MAX and vc.stride() == kc.stride()
+                 and 256 % D == 0)
+        if fused:
+            return self.ops.linear_rope(h, w, self.quant, self.cos, self.sin, pos0, B, T, self.hq, self.hkv, D, kc, vc)
+        return self.ops.rope_append(self._lin(h, w), self.cos, self.sin, pos0, B, T, self.hq, self.hkv, D, kc, vc)
+
     def _fused_push(self) -> bool:
         """Whether the kernel that finishes a sharded op's output pushes it to the peers itself (BI_FUSED_PUSH=0
         keeps the separate gather kernel)."""
@@ -366,8 +397,7 @@ class ShardedDecoder:
         scale = 1.0 / math.sqrt(D)
         h = self.ops.rms_norm(x, self.layers[0]["n1"], cfg.eps)
         for li, L in enumerate(self.layers):
-            q = self.ops.rope_append(self._lin(h, L["qkv"]), self.cos, self.sin, pos0, B, T, self.hq, self.hkv, D,
-                                     self.kc[li], self.vc[li])
+            q = self._qkv(h, L["qkv"], pos0, B, T, self.kc[li], self.vc[li])
             kk, vv = self.kc[li][:B, :, :end], self.vc[li][:B, :, :end]
             if T == 1:
                 a, aw = self._attend_gather(q, kk, vv, scale)
@@ -416,7 +446,7 @@ class GraphedDecoder:
         x = m.embed[self.tokens.reshape(-1)]
         h = m.ops.rms_norm(x, m.layers[0]["n1"], cfg.eps)
         for li, L in enumerate(m.layers):
-            q = m.ops.rope_append(m._lin(h, L["qkv"]), m.cos, m.sin, self.pos, B, 1, m.hq, m.hkv, D, m.kc[li], m.vc[li])
+            q = m._qkv(h, L["qkv"], self.pos, B, 1, m.kc[li], m.vc[li])
             a, aw = m._attend_gather(q, m.kc[li][:B], m.vc[li][:B], scale, kv_lens=self.lens)
             x, h = m.ops.add_rms_norm(x, m._lin(a, L["o"], aw), L["n2"], cfg.eps)
             act, aw = m._gated(m._lin(h, L["gu"]))

@@ -129,6 +129,49 @@ def test_cache_append_past_capacity_writes_nothing_and_reports(bi):
 
 
 @pytest.mark.parametrize("quant", [None, (4, 64)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_qkv_fold_that_rotates_and_appends_equals_the_separate_kernels(bi, dt, quant):
+    """bi_matmul_rope / bi_qmm_rope: the projection's fold kernel applies the rotary embedding and writes the
+    cache. q, the K cache and the V cache must carry the bits of matmul followed by bi_rope_append -- for a
+    prefill (T > 1), a decode step (T = 1), and with tokens past the capacity (skipped, status word set)."""
+    from mlx_batch_invariant_b200 import _lib
+    from mlx_batch_invariant_b200.runner.decoder import KernelBackend, quantize_rows
+    ops = KernelBackend()
+    hq, hkv, D, Kd, cap = 4, 2, 64, 512, 24
+    g = torch.Generator().manual_seed(11)
+    W = (torch.randn((hq + 2 * hkv) * D, Kd, generator=g) / 16).to(dt).cuda()
+    w = W if quant is None else quantize_rows(W, quant[1], quant[0])
+    cos = torch.rand(cap, D, generator=g).cuda()
+    sin = torch.rand(cap, D, generator=g).cuda()
+    bits = lambda t: t.contiguous().view(torch.int16).cpu()
+    bi.check_device_status()
+    for B, T, start in ((3, 5, 7), (16, 1, 9), (1, 1, 0), (2, 4, cap - 2)):
+        x = torch.randn(B * T, Kd, generator=g).to(dt).cuda()
+        pos0 = torch.tensor([start], dtype=torch.long, device="cuda")
+        caches = [torch.full((B, hkv, cap, D), 3.0, dtype=dt, device="cuda") for _ in range(4)]
+        if quant is None:
+            qkv = bi.batch_invariant_matmul(x, W.T)
+        else:
+            qkv = bi.batch_invariant_quantized_matmul(x, *w, group_size=quant[1], bits=quant[0])
+        q1 = ops.rope_append(qkv, cos, sin, pos0, B, T, hq, hkv, D, caches[0], caches[1])
+        overflow = start + T > cap
+        if overflow:
+            with pytest.raises(_lib.KernelError, match="0x3"):
+                bi.check_device_status()
+        q2 = ops.linear_rope(x, w, quant, cos, sin, pos0, B, T, hq, hkv, D, caches[2], caches[3])
+        if overflow:
+            with pytest.raises(_lib.KernelError, match="0x3"):
+                bi.check_device_status()
+            valid = cap - start                                  # tokens that fit: only their q rows were written
+            assert torch.equal(bits(q1[:, :, :valid]), bits(q2[:, :, :valid]))
+        else:
+            assert torch.equal(bits(q1), bits(q2))
+        assert torch.equal(bits(caches[0]), bits(caches[2])) and torch.equal(bits(caches[1]), bits(caches[3]))
+        assert bool((caches[2][:, :, start:min(start + T, cap)] != 3).any())
+    bi.check_device_status()
+
+
+@pytest.mark.parametrize("quant", [None, (4, 64)])
 def test_full_size_llama3_8b_row0_is_batch_invariant(bi, quant):
     """The configured model at full size (32 layers, d 4096, 32/8 heads, ffn 14336, vocab 128 256; random init):
     row 0 carries the same prompt at batch 1, 4, 16 and 64; its logits after the prefill and after each of two
