@@ -105,7 +105,6 @@ class KernelBackend(TorchGlue):
 
     def linear_rope(self, x, w, quant, cos, sin, pos0, B, T, hq, hkv, D, kc, vc):
         """rope_append(linear(x, w)) in the matmul's own two launches: returns the rotated q [B, hq, T, D]."""
-        from .. import _lib  # noqa: F401  (the library must be loadable)
         q = torch.empty(B, hq, T, D, dtype=x.dtype, device=x.device)
         rope = (cos.data_ptr(), sin.data_ptr(), pos0.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T, hq, hkv, D,
                 kc.stride(0), kc.stride(1), kc.stride(2), min(kc.shape[2], cos.shape[0]))
