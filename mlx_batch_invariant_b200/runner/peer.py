@@ -75,15 +75,15 @@ class PushGather:
                 except _lib.KernelError as e:           # no peer mapping to rank r from here (no NVLink / IPC between the two)
                     failure = failure or f"rank {rank} cannot map rank {r}'s buffer: {e}"
                 self.bases.append(p.value)
-            # Every rank must come to the same verdict, or the ones that succeeded would wait for the others forever.
-            verdicts = [None] * world
-            dist.all_gather_object(verdicts, failure, group=group)
-            if any(verdicts):
+            # Every rank must reach the same conclusion, or the ones that succeeded would wait for the others forever.
+            outcomes = [None] * world
+            dist.all_gather_object(outcomes, failure, group=group)
+            if any(outcomes):
                 for r, b in enumerate(self.bases):
                     if r != rank and b:
                         self.lib.bi_peer_close(ctypes.c_void_p(b))
                 self.lib.bi_peer_free(base)
-                raise PeerUnavailable("; ".join(v for v in verdicts if v))
+                raise PeerUnavailable("; ".join(v for v in outcomes if v))
             self.own = [torch.as_tensor(_Raw(base.value + b * self.cap, self.cap), device=device) for b in range(NBUF)]
             self.counters = torch.zeros(2, dtype=torch.int32, device=device)
         self.calls = 0
