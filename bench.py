@@ -769,7 +769,10 @@ def run_reference(args):
         sample = f"first {rows} of {wl_cls.M} rows per step"
         cfg = {"workload": wl_cls.name, "M": wl_cls.M, "N": wl_cls.N, "K": wl_cls.K}
     else:
-        raise SystemExit(f"--impl reference: workload {args.workload} not wired")
+        # the contract's fallback line: this workload's CPU leg is its `cpu_baseline` only
+        print(json.dumps({"impl": "reference", "unavailable": f"no reference arm for workload {args.workload}: its CPU "
+                                                              f"restatement is timed as cpu_baseline in the default arm"}))
+        return
     v = statistics.mean(vals)
     line = {"impl": "reference", "metric": wl_cls.metric, "value": round(v, 6), "unit": wl_cls.unit,
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
