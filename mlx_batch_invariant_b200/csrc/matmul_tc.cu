@@ -3,18 +3,19 @@
 //
 // Canonical order per output element (what never changes with M):
 //   * K is cut into groups of 256. Inside a group the tensor core runs sixteen
-//     MMA steps of K = 16 in ascending k, all of the one instruction shape
-//     tcgen05.mma.cta_group::1.kind::f16  M=128 (weight rows) x N=128 (batch rows) x K=16,
-//     operands in the input dtype, fp32 accumulator. The first step of a group
-//     overwrites the accumulator (accumulate off), so a group partial starts
-//     from nothing.
+//     MMA steps of K = 16 in ascending k,
+//     tcgen05.mma.cta_group::1.kind::f16  M=128 (weight rows) x N (batch rows) x K=16,
+//     operands in the input dtype, fp32 accumulator. N is the batch tile's row
+//     count rounded up to 16 (16 ... 128): an accumulator column depends on its
+//     own batch row only, and the tests compare every N the kernel can issue
+//     with the bits of a batch of one. The first step of a group overwrites the
+//     accumulator (accumulate off), so a group partial starts from nothing.
 //   * out = T(((0 + p_0) + p_1) + ... ), plain fp32 adds of the group partials,
 //     g ascending, one rounding at the end.
-// The weight is the 128-row "A" operand and the batch is the 128-column "B"
-// operand, so a decode step with one row still issues exactly the instruction a
-// 128-row prefill tile issues; batch rows beyond M are never loaded (their
-// accumulator columns hold garbage that is never read -- every accumulator
-// column depends on its own batch row only).
+// The weight is the 128-row "A" operand and the batch is the "B" operand, so a
+// decode step with one row issues the instruction of a 16-row tile; batch rows
+// beyond M are never loaded (their accumulator columns hold garbage that is
+// never read).
 //
 // Launch shapes (same arithmetic, reference: mlx_batch_invariant/kernels/matmul.py:279-314):
 //   split : one job per (weight tile, batch tile, K group); the raw fp32 group
